@@ -1,0 +1,151 @@
+/* C ABI of the B200 MatXtract SpMV library (libmatxtract_b200.so).
+ *
+ * This is the layer the C++ host API (include/MatXtract.h) and the command-line drivers call CUDA
+ * through, and what a foreign-language binding (ctypes, cgo, JNI ...) would bind.  Plain C types only;
+ * every function returns an int status (MX_OK = 0), never throws and never exits the process.
+ * Host buffers belong to the caller; device buffers belong to the handle.  One thread per handle.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the reference project).
+ */
+#ifndef MX_CAPI_H
+#define MX_CAPI_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    MX_OK = 0,
+    MX_ERR_INVALID = 1,  /* bad argument (null pointer, negative size, non-square matrix for a partition ...) */
+    MX_ERR_CUDA = 2,     /* a CUDA runtime call failed; see mx_last_error_string */
+    MX_ERR_TAU = 3,      /* tau_c < tau_r, or a threshold that no prefix of the ranking reaches */
+    MX_ERR_STATE = 4,    /* call order: no matrix uploaded, no partition built ... */
+    MX_ERR_OVERFLOW = 5, /* a count does not fit the reference's int32 index type */
+    MX_ERR_TIMEOUT = 6,  /* a bounded device-side wait ran out */
+    MX_ERR_NOMEM = 7,
+    MX_ERR_NO_DEVICE = 8 /* no CUDA device: there is no CPU fallback */
+};
+
+/* Value type of a handle.  The reference fixes it at compile time (-Dfp64, include/common.h:53-70):
+ * MX_FP64 = double values, 8x4 fragments, 32-bit bitmaps; MX_FP16 = half values, 8x8 fragments, 64-bit bitmaps. */
+enum { MX_FP64 = 0, MX_FP16 = 1 };
+
+typedef struct mx_handle_s *mx_handle_t;
+
+int mx_version(void);
+const char *mx_status_string(int status);
+
+/* ---- handle --------------------------------------------------------------------------------------- */
+int mx_create(mx_handle_t *h, int device, int dtype);
+int mx_destroy(mx_handle_t h);
+const char *mx_last_error_string(mx_handle_t h);
+/* The CUDA stream (cudaStream_t) all work of this handle is issued on. */
+void *mx_stream(mx_handle_t h);
+int mx_sync(mx_handle_t h);
+
+/* Uploads a host CSR matrix (replaces the per-call cudaMalloc + cudaMemcpy of every reference wrapper,
+ * e.g. src/spmv_kernel/cdSpMV.cu:407-418).  Any previous matrix and partition of the handle is dropped. */
+int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind,
+                  const void *val);
+
+/* ---- extraction (preprocessing) ------------------------------------------------------------------- */
+typedef struct {
+    int dCols, nnzColD, sCols, nnzColS; /* tau_c cut,  test/test_autotc_spmv.cpp:1131-1145 */
+    int dRows, nnzRowD, sRows, nnzRowS; /* tau_r cut,  test/test_autotc_spmv.cpp:1249-1269 */
+    int chunkNum, totalFrags;           /* 8-row panels and fragments, :1354,:1375 */
+    int nnzCD;                          /* residual CSR entries, :1477 */
+    int fragK;                          /* 4 (FP64) or 8 (FP16) */
+    double tc_nnz_ratio;                /* nnzRowD / (totalFrags * 8 * fragK), :1376 */
+    float preprocess_ms;                /* device time of the whole extraction */
+    int active;                         /* 0 when tau = (0,0): no extraction, the residual is the input CSR (:1106,:1638) */
+} mx_partition_stats;
+
+/* Runs the cascaded extraction on the device: column histogram and tau_c hot-column selection, row
+ * ranking inside the hot columns and tau_r hot-row selection, dense 8xK tile construction, residual CSR
+ * compaction.  Replaces the host pipeline inside main() of test/test_autotc_spmv.cpp:1119-1421,1486-1492
+ * and its three cuSPARSE transposes (utilities/csr2csc.cpp).  tau_c and tau_r are converted to float
+ * exactly as the reference does (:1103-1104); tau_c < tau_r is rejected (:1064-1069) with MX_ERR_TAU. */
+int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats);
+int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats);
+
+/* Host destinations for the arrays of the partition, in the reference's layout; a NULL member is skipped.
+ * Sizes follow from mx_partition_stats (K = fragK). */
+typedef struct {
+    int *xperm;      /* [n_cols]  x_CD[i] = x[xperm[i]]; first dCols entries = hot columns in rank order */
+    int *rId;        /* [dRows]   original row of hot row i */
+    int *rowPtr_dd;  /* [dRows+1] core-dense block as CSR, column ids = density ranks */
+    int *colInd_dd;  /* [nnzRowD] */
+    void *val_dd;    /* [nnzRowD] */
+    int *chunkPtr;   /* [chunkNum+1] */
+    int *AToX;       /* [totalFrags*K] sparse_AToX_index */
+    int *fragPtr;    /* [totalFrags+1] */
+    void *fragBit;   /* [totalFrags] uint32 (FP64) or uint64 (FP16) */
+    void *tcVal;     /* [nnzRowD] */
+    int *rowPtr_CD;  /* [n_rows+1] residual CSR */
+    int *colInd_CD;  /* [nnzCD] */
+    void *val_CD;    /* [nnzCD] */
+} mx_partition_arrays;
+int mx_download_partition(mx_handle_t h, const mx_partition_arrays *out);
+
+/* ---- execution ------------------------------------------------------------------------------------ */
+/* y = A x with x and y DEVICE pointers in the matrix's original column / row order; asynchronous on the
+ * handle's stream.  Runs the tile kernel on the core-dense block and the CSR kernel on the residual; the
+ * second produces the final y, so there is no merge pass and no host scatter
+ * (replaces test/test_autotc_spmv.cpp:1507-1559). */
+int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev);
+/* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
+int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
+/* Timing loop on the device: `warm` untimed and `iters` timed repetitions (the reference uses 200 and
+ * 4000, src/spmv_kernel/cdSpMV.cu:454-455).  ms_tile / ms_resid time each half alone, as the reference's
+ * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */
+int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile,
+                  float *ms_resid, float *ms_total);
+/* Number of kernel launches one mx_spmv issues for the current matrix / partition. */
+int mx_spmv_launches(mx_handle_t h);
+/* Device error word of the last kernels (0 = none). */
+int mx_device_error(mx_handle_t h, int *err);
+
+/* ---- stateless mirrors of include/MatXtract.h (host pointers in and out, synchronous) -------------- */
+/* cdspmv (include/MatXtract.h:3-5, src/spmv_kernel/cdSpMV.cu:395-491): y += A x on the CUDA cores; y is in/out. */
+int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColInd, const void *x, void *y,
+              int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv, double *pre_ms);
+/* du_tcspmv_fp64 / du_tcspmv_fp16_v2 (include/MatXtract.h:7-9,26-28): fragment-format SpMV on the tensor cores.
+ * FP64: y is in/out (the reference preloads it and adds, du_tcSpMV_fp64.cu:296,334); FP16: y is overwritten
+ * (du_tcSpMV_fp16_v2.cu:150,187). */
+int mx_du_tcspmv(int dtype, const int *chunkPtr, const int *fragPtr, const void *fragBit, const void *tcVal,
+                 int n_vals, const int *sparse_AToX_index, const void *x, void *y, int dRows, int dCols, int warm,
+                 int iters, double *ms_per_spmv);
+/* se_tcspmv_fp64 / se_tcspmv_fp16 (include/MatXtract.h:14-15,30-31): SpMV of the core-dense block given as CSR.
+ * Y_val[i] is the result for input row order_rid[i]; this implementation returns the identity order. */
+int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColIdx, const void *x, void *y,
+                 int *order_rid, int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv);
+
+/* ---- synthetic inputs (host code) ----------------------------------------------------------------- */
+enum { MX_SYNTH_UNIFORM = 0, MX_SYNTH_POWERLAW = 1, MX_SYNTH_BLOCK = 2, MX_SYNTH_HOTCOL = 3 };
+typedef struct {
+    int kind;
+    int64_t n;            /* square dimension */
+    uint64_t seed;
+    double mean_len;      /* UNIFORM: Poisson mean; HOTCOL: mean row length (1 + geometric) */
+    double zipf_s;        /* POWERLAW: exponent of the row-length law */
+    double alpha;         /* POWERLAW: length = clip(ceil(alpha * K), 1, max_len) */
+    int64_t max_len;      /* POWERLAW: clip */
+    double local_frac;    /* POWERLAW: share of a row's columns within +-local_halfwidth of the row index */
+    int64_t local_halfwidth; /* POWERLAW: columns; BLOCK: block columns */
+    int blocks_per_row;   /* BLOCK: dense 8x8 blocks per block row */
+    double hot_col_frac;  /* HOTCOL: share of columns that are hot */
+    double hot_nnz_frac;  /* HOTCOL: share of entries drawn from the hot columns */
+    int normal_values;    /* values ~ N(0,1) instead of U(-1,1) */
+} mx_synth_params;
+/* Row pointers (relative to row_begin) of rows [row_begin, row_end); row_ptr_out has row_end-row_begin+1 ints. */
+int mx_synth_row_lengths(const mx_synth_params *p, int64_t row_begin, int64_t row_end, int *row_ptr_out);
+int mx_synth_fill(const mx_synth_params *p, int dtype, int64_t row_begin, int64_t row_end, const int *row_ptr,
+                  int *col_ind, void *val);
+int mx_synth_vector(uint64_t seed, int dtype, int64_t begin, int64_t end, void *x);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MX_CAPI_H */

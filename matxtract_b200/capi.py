@@ -1,0 +1,240 @@
+"""ctypes binding of the C ABI in ``include/mx_capi.h`` (the same stub a foreign host language would write)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+FP64, FP16 = 0, 1
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
+
+STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
+          6: "MX_ERR_TIMEOUT", 7: "MX_ERR_NOMEM", 8: "MX_ERR_NO_DEVICE"}
+
+
+class MxError(RuntimeError):
+    def __init__(self, status: int, msg: str = ""):
+        self.status = status
+        super().__init__(f"{STATUS.get(status, status)}: {msg}")
+
+
+class PartitionStats(C.Structure):
+    _fields_ = [("dCols", C.c_int), ("nnzColD", C.c_int), ("sCols", C.c_int), ("nnzColS", C.c_int),
+                ("dRows", C.c_int), ("nnzRowD", C.c_int), ("sRows", C.c_int), ("nnzRowS", C.c_int),
+                ("chunkNum", C.c_int), ("totalFrags", C.c_int), ("nnzCD", C.c_int), ("fragK", C.c_int),
+                ("tc_nnz_ratio", C.c_double), ("preprocess_ms", C.c_float), ("active", C.c_int)]
+
+    def as_dict(self):
+        return {k: getattr(self, k) for k, _ in self._fields_}
+
+
+class _PartitionArrays(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("xperm", "rId", "rowPtr_dd", "colInd_dd", "val_dd", "chunkPtr", "AToX",
+                                           "fragPtr", "fragBit", "tcVal", "rowPtr_CD", "colInd_CD", "val_CD")]
+
+
+class SynthParams(C.Structure):
+    _fields_ = [("kind", C.c_int), ("n", C.c_int64), ("seed", C.c_uint64), ("mean_len", C.c_double),
+                ("zipf_s", C.c_double), ("alpha", C.c_double), ("max_len", C.c_int64), ("local_frac", C.c_double),
+                ("local_halfwidth", C.c_int64), ("blocks_per_row", C.c_int), ("hot_col_frac", C.c_double),
+                ("hot_nnz_frac", C.c_double), ("normal_values", C.c_int)]
+
+
+# every symbol include/mx_capi.h declares: name -> (restype, argtypes)
+_vp, _i, _d = C.c_void_p, C.c_int, C.c_double
+_ip = C.POINTER(C.c_int)
+SYMBOLS = {
+    "mx_version": (_i, []),
+    "mx_status_string": (C.c_char_p, [_i]),
+    "mx_create": (_i, [C.POINTER(_vp), _i, _i]),
+    "mx_destroy": (_i, [_vp]),
+    "mx_last_error_string": (C.c_char_p, [_vp]),
+    "mx_stream": (_vp, [_vp]),
+    "mx_sync": (_i, [_vp]),
+    "mx_upload_csr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
+    "mx_partition": (_i, [_vp, _d, _d, C.POINTER(PartitionStats)]),
+    "mx_partition_stats_get": (_i, [_vp, C.POINTER(PartitionStats)]),
+    "mx_download_partition": (_i, [_vp, C.POINTER(_PartitionArrays)]),
+    "mx_spmv": (_i, [_vp, _vp, _vp]),
+    "mx_spmv_host": (_i, [_vp, _vp, _vp]),
+    "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mx_spmv_launches": (_i, [_vp]),
+    "mx_device_error": (_i, [_vp, _ip]),
+    "mx_cdspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d), C.POINTER(_d)]),
+    "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
+    "mx_se_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d)]),
+    "mx_synth_row_lengths": (_i, [C.POINTER(SynthParams), C.c_int64, C.c_int64, _vp]),
+    "mx_synth_fill": (_i, [C.POINTER(SynthParams), _i, C.c_int64, C.c_int64, _vp, _vp, _vp]),
+    "mx_synth_vector": (_i, [C.c_uint64, _i, C.c_int64, C.c_int64, _vp]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libmatxtract_b200.so (built in-tree by ``python -m matxtract_b200.build``).  No fallback."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is missing: run `python -m matxtract_b200.build` (there is no CPU path)")
+        L = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def np_dtype(dtype: int):
+    return np.float64 if dtype == FP64 else np.float16
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data_as(C.c_void_p)
+    if hasattr(a, "data_ptr"):  # torch tensor
+        return C.c_void_p(a.data_ptr())
+    return C.c_void_p(int(a))
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+class MatXtract:
+    """One matrix on one GPU: upload, extract with (tau_c, tau_r), multiply.
+
+    Mirrors what ``matxtract_perftest`` does inside its ``main()`` (reference test/test_autotc_spmv.cpp:1050-1669)
+    as a reusable object.
+    """
+
+    def __init__(self, dtype: int = FP64, device: int = 0):
+        self._h = C.c_void_p()
+        self.dtype = dtype
+        self.device = device
+        st = lib().mx_create(C.byref(self._h), device, dtype)
+        if st != 0:
+            raise MxError(st, lib().mx_status_string(st).decode())
+        self.n_rows = self.n_cols = self.nnz = 0
+        self.stats = None
+
+    def _ck(self, st):
+        if st != 0:
+            raise MxError(st, lib().mx_last_error_string(self._h).decode())
+
+    def close(self):
+        if self._h:
+            lib().mx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload_csr(self, n_rows, n_cols, row_ptr, col_ind, val):
+        row_ptr, col_ind, val = _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(val, np_dtype(self.dtype))
+        nnz = int(col_ind.shape[0])
+        self._ck(lib().mx_upload_csr(self._h, n_rows, n_cols, nnz, _ptr(row_ptr), _ptr(col_ind), _ptr(val)))
+        self.n_rows, self.n_cols, self.nnz = n_rows, n_cols, nnz
+
+    def partition(self, tau_c: float = 0.0, tau_r: float = 0.0) -> PartitionStats:
+        st = PartitionStats()
+        self._ck(lib().mx_partition(self._h, float(tau_c), float(tau_r), C.byref(st)))
+        self.stats = st
+        return st
+
+    def download_partition(self) -> dict:
+        s = self.stats
+        vdt = np_dtype(self.dtype)
+        bdt = np.uint32 if self.dtype == FP64 else np.uint64
+        out = {
+            "xperm": np.empty(self.n_cols, np.int32), "rId": np.empty(s.dRows, np.int32),
+            "rowPtr_dd": np.empty(s.dRows + 1, np.int32), "colInd_dd": np.empty(s.nnzRowD, np.int32),
+            "val_dd": np.empty(s.nnzRowD, vdt), "chunkPtr": np.empty(s.chunkNum + 1, np.int32),
+            "AToX": np.empty(s.totalFrags * s.fragK, np.int32), "fragPtr": np.empty(s.totalFrags + 1, np.int32),
+            "fragBit": np.empty(s.totalFrags, bdt), "tcVal": np.empty(s.nnzRowD, vdt),
+            "rowPtr_CD": np.empty(self.n_rows + 1, np.int32), "colInd_CD": np.empty(s.nnzCD, np.int32),
+            "val_CD": np.empty(s.nnzCD, vdt),
+        }
+        arr = _PartitionArrays(**{k: _ptr(v) for k, v in out.items()})
+        self._ck(lib().mx_download_partition(self._h, C.byref(arr)))
+        return out
+
+    def spmv(self, x_dev, y_dev):
+        """x_dev / y_dev: device pointers (ints) or torch CUDA tensors; asynchronous on ``self.stream``."""
+        self._ck(lib().mx_spmv(self._h, _ptr(x_dev), _ptr(y_dev)))
+
+    def spmv_host(self, x: np.ndarray, y: np.ndarray | None = None) -> np.ndarray:
+        x = _c(x, np_dtype(self.dtype))
+        if y is None:
+            y = np.empty(self.n_rows, np_dtype(self.dtype))
+        self._ck(lib().mx_spmv_host(self._h, _ptr(x), _ptr(y)))
+        return y
+
+    def spmv_timed(self, x_dev, y_dev, warm=20, iters=200):
+        t, r, a = C.c_float(), C.c_float(), C.c_float()
+        self._ck(lib().mx_spmv_timed(self._h, _ptr(x_dev), _ptr(y_dev), warm, iters, C.byref(t), C.byref(r), C.byref(a)))
+        return {"ms_tile": t.value, "ms_resid": r.value, "ms_total": a.value}
+
+    @property
+    def stream(self) -> int:
+        return lib().mx_stream(self._h) or 0
+
+    @property
+    def launches_per_spmv(self) -> int:
+        return lib().mx_spmv_launches(self._h)
+
+    def sync(self):
+        self._ck(lib().mx_sync(self._h))
+
+    def device_error(self) -> int:
+        e = C.c_int()
+        self._ck(lib().mx_device_error(self._h, C.byref(e)))
+        return e.value
+
+
+def _raise(st):
+    if st != 0:
+        raise MxError(st, lib().mx_status_string(st).decode())
+
+
+def cdspmv(dtype, val, row_ptr, col_ind, x, y, warm=0, iters=0):
+    """y += A x (host arrays).  Mirror of the reference's cdspmv (include/MatXtract.h:3-5)."""
+    vdt = np_dtype(dtype)
+    val, row_ptr, col_ind, x = _c(val, vdt), _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(x, vdt)
+    y = np.array(y, dtype=vdt, copy=True)
+    ms, pre = C.c_double(), C.c_double()
+    _raise(lib().mx_cdspmv(dtype, _ptr(val), _ptr(row_ptr), _ptr(col_ind), _ptr(x), _ptr(y), len(row_ptr) - 1, len(x),
+                           len(col_ind), warm, iters, C.byref(ms), C.byref(pre)))
+    return y, ms.value, pre.value
+
+
+def du_tcspmv(dtype, chunkPtr, fragPtr, fragBit, tcVal, AToX, x_d, y, dRows, warm=0, iters=0):
+    """Fragment-format SpMV (host arrays).  Mirror of du_tcspmv_fp64 / du_tcspmv_fp16_v2."""
+    vdt = np_dtype(dtype)
+    bdt = np.uint32 if dtype == FP64 else np.uint64
+    chunkPtr, fragPtr, AToX = _c(chunkPtr, np.int32), _c(fragPtr, np.int32), _c(AToX, np.int32)
+    fragBit, tcVal, x_d = _c(fragBit, bdt), _c(tcVal, vdt), _c(x_d, vdt)
+    y = np.array(y, dtype=vdt, copy=True)
+    ms = C.c_double()
+    _raise(lib().mx_du_tcspmv(dtype, _ptr(chunkPtr), _ptr(fragPtr), _ptr(fragBit), _ptr(tcVal), len(tcVal), _ptr(AToX),
+                              _ptr(x_d), _ptr(y), dRows, len(x_d), warm, iters, C.byref(ms)))
+    return y, ms.value
+
+
+def se_tcspmv(dtype, val, row_ptr, col_ind, x_d, warm=0, iters=0):
+    """SpMV of a core-dense block given as CSR (host arrays).  Mirror of se_tcspmv_fp64 / se_tcspmv_fp16."""
+    vdt = np_dtype(dtype)
+    val, row_ptr, col_ind, x_d = _c(val, vdt), _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(x_d, vdt)
+    rows = len(row_ptr) - 1
+    y = np.zeros(rows, vdt)
+    order = np.empty(rows, np.int32)
+    ms = C.c_double()
+    _raise(lib().mx_se_tcspmv(dtype, _ptr(val), _ptr(row_ptr), _ptr(col_ind), _ptr(x_d), _ptr(y), _ptr(order), rows,
+                              len(x_d), len(col_ind), warm, iters, C.byref(ms)))
+    return y, order, ms.value

@@ -1,0 +1,558 @@
+// C ABI of libmatxtract_b200.so: handle management, matrix upload, extraction, SpMV, timing loops, and the
+// stateless mirrors of the reference's host API (include/MatXtract.h).  See include/mx_capi.h.
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "mx_internal.h"
+
+using namespace mx;
+
+struct mx_handle_s {
+    int device = 0, dtype = MX_FP64;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    // input matrix
+    bool has_matrix = false;
+    int n_rows = 0, n_cols = 0, nnz = 0;
+    int *row_ptr = nullptr, *col_ind = nullptr;
+    void *val = nullptr;
+    // extraction
+    bool planned = false;  // some plan (with or without partition) is ready for mx_spmv
+    mx_partition_stats stats{};
+    PartArrays part;
+    ResidPlan resid;
+    TilePlan tile;
+    void *ytile = nullptr;   // [n_rows] accumulate-type carrier of the tile half
+    void *x_perm = nullptr;  // [n_cols] x in partition order
+    // staging for the host-pointer entry point
+    void *x_stage = nullptr, *y_stage = nullptr;
+    int *dev_err = nullptr;
+
+    int fail(int status, const std::string &msg) {
+        err = msg;
+        return status;
+    }
+    int cuda_fail(cudaError_t e, const char *what) {
+        err = std::string(what) + ": " + cudaGetErrorString(e);
+        return MX_ERR_CUDA;
+    }
+};
+
+#define HCK(call)                                               \
+    do {                                                        \
+        cudaError_t e_ = (call);                                \
+        if (e_ != cudaSuccess) return h->cuda_fail(e_, #call);  \
+    } while (0)
+
+namespace {
+
+void drop_plan(mx_handle_t h) {
+    resid_plan_free(h->resid);
+    tile_plan_free(h->tile);
+    part_arrays_free(h->part);
+    cudaFree(h->ytile);
+    cudaFree(h->x_perm);
+    h->ytile = h->x_perm = nullptr;
+    h->planned = false;
+    h->stats = mx_partition_stats{};
+}
+
+void drop_matrix(mx_handle_t h) {
+    drop_plan(h);
+    cudaFree(h->row_ptr);
+    cudaFree(h->col_ind);
+    cudaFree(h->val);
+    cudaFree(h->x_stage);
+    cudaFree(h->y_stage);
+    h->row_ptr = h->col_ind = nullptr;
+    h->val = h->x_stage = h->y_stage = nullptr;
+    h->has_matrix = false;
+}
+
+int check_device() {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return MX_ERR_NO_DEVICE;
+    }
+    return MX_OK;
+}
+
+}  // namespace
+
+namespace {
+struct DevBufs {  // frees on scope exit
+    void *p[16] = {};
+    int n = 0;
+    template <typename T>
+    cudaError_t up(T **d, const void *src, size_t bytes) {
+        cudaError_t e = cudaMalloc((void **)d, bytes > 0 ? bytes : 1);
+        if (e != cudaSuccess) return e;
+        p[n++] = *d;
+        if (src && bytes > 0) e = cudaMemcpy(*d, src, bytes, cudaMemcpyHostToDevice);
+        return e;
+    }
+    ~DevBufs() {
+        for (int i = 0; i < n; ++i) cudaFree(p[i]);
+    }
+};
+}  // namespace
+
+extern "C" {
+
+int mx_version(void) { return 100; }
+
+const char *mx_status_string(int status) {
+    switch (status) {
+        case MX_OK: return "ok";
+        case MX_ERR_INVALID: return "invalid argument";
+        case MX_ERR_CUDA: return "CUDA error";
+        case MX_ERR_TAU: return "invalid tau (tau_c < tau_r, or a threshold no prefix reaches)";
+        case MX_ERR_STATE: return "call out of order";
+        case MX_ERR_OVERFLOW: return "count exceeds int32";
+        case MX_ERR_TIMEOUT: return "bounded device wait ran out";
+        case MX_ERR_NOMEM: return "out of memory";
+        case MX_ERR_NO_DEVICE: return "no CUDA device (this library has no CPU fallback)";
+    }
+    return "unknown status";
+}
+
+int mx_create(mx_handle_t *out, int device, int dtype) {
+    if (!out || (dtype != MX_FP64 && dtype != MX_FP16)) return MX_ERR_INVALID;
+    *out = nullptr;
+    int st = check_device();
+    if (st != MX_OK) return st;
+    if (cudaSetDevice(device) != cudaSuccess) {
+        cudaGetLastError();
+        return MX_ERR_INVALID;
+    }
+    mx_handle_t h = new mx_handle_s;
+    h->device = device;
+    h->dtype = dtype;
+    if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&h->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(h->dev_err, 0, sizeof(int)) != cudaSuccess) {
+        delete h;
+        return MX_ERR_CUDA;
+    }
+    *out = h;
+    return MX_OK;
+}
+
+int mx_destroy(mx_handle_t h) {
+    if (!h) return MX_ERR_INVALID;
+    cudaSetDevice(h->device);
+    cudaStreamSynchronize(h->stream);
+    drop_matrix(h);
+    cudaFree(h->dev_err);
+    cudaStreamDestroy(h->stream);
+    delete h;
+    return MX_OK;
+}
+
+const char *mx_last_error_string(mx_handle_t h) { return h ? h->err.c_str() : "null handle"; }
+void *mx_stream(mx_handle_t h) { return h ? (void *)h->stream : nullptr; }
+
+int mx_sync(mx_handle_t h) {
+    if (!h) return MX_ERR_INVALID;
+    HCK(cudaSetDevice(h->device));
+    HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind,
+                  const void *val) {
+    if (!h) return MX_ERR_INVALID;
+    if (n_rows < 0 || n_cols < 0 || nnz < 0 || !row_ptr || (nnz > 0 && (!col_ind || !val)))
+        return h->fail(MX_ERR_INVALID, "mx_upload_csr: bad sizes or null arrays");
+    if (row_ptr[0] != 0 || row_ptr[n_rows] != nnz) return h->fail(MX_ERR_INVALID, "mx_upload_csr: row_ptr ends != nnz");
+    HCK(cudaSetDevice(h->device));
+    drop_matrix(h);
+    const size_t vb = val_bytes(h->dtype);
+    HCK(cudaMalloc(&h->row_ptr, sizeof(int) * ((size_t)n_rows + 1)));
+    HCK(cudaMalloc(&h->col_ind, sizeof(int) * (size_t)(nnz > 0 ? nnz : 1)));
+    HCK(cudaMalloc(&h->val, vb * (size_t)(nnz > 0 ? nnz : 1)));
+    HCK(cudaMalloc(&h->x_stage, vb * (size_t)(n_cols > 0 ? n_cols : 1)));
+    HCK(cudaMalloc(&h->y_stage, vb * (size_t)(n_rows > 0 ? n_rows : 1)));
+    HCK(cudaMemcpyAsync(h->row_ptr, row_ptr, sizeof(int) * ((size_t)n_rows + 1), cudaMemcpyHostToDevice, h->stream));
+    if (nnz > 0) {
+        HCK(cudaMemcpyAsync(h->col_ind, col_ind, sizeof(int) * (size_t)nnz, cudaMemcpyHostToDevice, h->stream));
+        HCK(cudaMemcpyAsync(h->val, val, vb * (size_t)nnz, cudaMemcpyHostToDevice, h->stream));
+    }
+    HCK(cudaStreamSynchronize(h->stream));
+    h->n_rows = n_rows;
+    h->n_cols = n_cols;
+    h->nnz = nnz;
+    h->has_matrix = true;
+    return MX_OK;
+}
+
+int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats) {
+    if (!h) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_partition: no matrix uploaded");
+    if (tau_c < tau_r) return h->fail(MX_ERR_TAU, "col_frac must be greater than hot_frac");
+    HCK(cudaSetDevice(h->device));
+    drop_plan(h);
+    const float colProp = (float)tau_c, rowProp = (float)tau_r;
+    cudaEvent_t e0, e1;
+    HCK(cudaEventCreate(&e0));
+    HCK(cudaEventCreate(&e1));
+    HCK(cudaEventRecord(e0, h->stream));
+    h->stats = mx_partition_stats{};
+    h->stats.fragK = frag_k(h->dtype);
+    if (rowProp == 0.0f && colProp == 0.0f) {
+        // tau = (0,0): the reference skips the extraction and runs cdspmv on the input CSR
+        h->resid.n_rows = h->n_rows;
+        h->resid.n_cols = h->n_cols;
+        h->resid.nnz = h->nnz;
+        h->resid.row_ptr = h->row_ptr;
+        h->resid.col_ind = h->col_ind;
+        h->resid.val = h->val;
+        HCK(resid_plan_build(h->dtype, h->resid, h->stream));
+        h->stats.nnzCD = h->nnz;
+        h->stats.sCols = h->n_cols;
+        h->stats.sRows = h->n_rows;
+        h->stats.nnzColS = h->nnz;
+    } else {
+        if (h->n_rows != h->n_cols) return h->fail(MX_ERR_INVALID, "mx_partition: the extraction needs a square matrix");
+        CsrDev A;
+        A.n_rows = h->n_rows;
+        A.n_cols = h->n_cols;
+        A.nnz = h->nnz;
+        A.row_ptr = h->row_ptr;
+        A.col_ind = h->col_ind;
+        A.val = h->val;
+        int status = MX_OK;
+        cudaError_t ce = partition_run(h->dtype, A, colProp, rowProp, h->part, h->stats, &status, h->stream);
+        if (ce != cudaSuccess) {
+            drop_plan(h);
+            return h->cuda_fail(ce, "partition_run");
+        }
+        if (status != MX_OK) {
+            drop_plan(h);
+            return h->fail(status, status == MX_ERR_TAU ? "tau threshold never reached by the ranking prefix"
+                                                        : "fragment count exceeds int32");
+        }
+        h->resid.n_rows = h->n_rows;
+        h->resid.n_cols = h->n_cols;
+        h->resid.nnz = h->stats.nnzCD;
+        h->resid.row_ptr = h->part.rowPtr_CD;
+        h->resid.col_ind = h->part.colInd_CD;
+        h->resid.val = h->part.val_CD;
+        HCK(resid_plan_build(h->dtype, h->resid, h->stream));
+        h->tile.A = h->part.tiles;
+        HCK(tile_plan_build(h->dtype, h->tile, h->stream));
+        HCK(cudaMalloc(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows));
+        HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
+        HCK(cudaMalloc(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols));
+    }
+    HCK(cudaEventRecord(e1, h->stream));
+    HCK(cudaEventSynchronize(e1));
+    float ms = 0;
+    HCK(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    h->stats.preprocess_ms = ms;
+    h->planned = true;
+    if (stats) *stats = h->stats;
+    return MX_OK;
+}
+
+int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats) {
+    if (!h || !stats) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "no partition");
+    *stats = h->stats;
+    return MX_OK;
+}
+
+int mx_download_partition(mx_handle_t h, const mx_partition_arrays *o) {
+    if (!h || !o) return MX_ERR_INVALID;
+    if (!h->planned || !h->stats.active) return h->fail(MX_ERR_STATE, "mx_download_partition: no active partition");
+    HCK(cudaSetDevice(h->device));
+    const mx_partition_stats &s = h->stats;
+    const size_t vb = val_bytes(h->dtype), bb = bit_bytes(h->dtype);
+    const int K = s.fragK;
+#define DL(dst, src, bytes)                                                                              \
+    do {                                                                                                 \
+        if ((dst) && (bytes) > 0) HCK(cudaMemcpyAsync((dst), (src), (bytes), cudaMemcpyDeviceToHost, h->stream)); \
+    } while (0)
+    DL(o->xperm, h->part.xperm, sizeof(int) * (size_t)h->n_cols);
+    DL(o->rId, h->part.rId, sizeof(int) * (size_t)s.dRows);
+    DL(o->rowPtr_dd, h->part.rowPtr_dd, sizeof(int) * ((size_t)s.dRows + 1));
+    DL(o->colInd_dd, h->part.colInd_dd, sizeof(int) * (size_t)s.nnzRowD);
+    DL(o->val_dd, h->part.val_dd, vb * (size_t)s.nnzRowD);
+    DL(o->chunkPtr, h->part.tiles.chunkPtr, sizeof(int) * ((size_t)s.chunkNum + 1));
+    DL(o->AToX, h->part.tiles.AToX, sizeof(int) * (size_t)s.totalFrags * K);
+    DL(o->fragPtr, h->part.tiles.fragPtr, sizeof(int) * ((size_t)s.totalFrags + 1));
+    DL(o->fragBit, h->part.tiles.fragBit, bb * (size_t)s.totalFrags);
+    DL(o->tcVal, h->part.tiles.tcVal, vb * (size_t)s.nnzRowD);
+    DL(o->rowPtr_CD, h->part.rowPtr_CD, sizeof(int) * ((size_t)h->n_rows + 1));
+    DL(o->colInd_CD, h->part.colInd_CD, sizeof(int) * (size_t)s.nnzCD);
+    DL(o->val_CD, h->part.val_CD, vb * (size_t)s.nnzCD);
+#undef DL
+    HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid) {
+    if (h->stats.active) {
+        HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
+        if (do_tile)
+            HCK(tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err, h->stream));
+        if (do_resid)
+            HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
+                           h->stream));
+    } else if (do_resid) {
+        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->dev_err, h->stream));
+    }
+    return MX_OK;
+}
+
+int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev) {
+    if (!h || !x_dev || !y_dev) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    return spmv_enqueue(h, x_dev, y_dev, true, true);
+}
+
+int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
+    if (!h || !x_host || !y_host) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_host: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    const size_t vb = val_bytes(h->dtype);
+    HCK(cudaMemcpyAsync(h->x_stage, x_host, vb * (size_t)h->n_cols, cudaMemcpyHostToDevice, h->stream));
+    int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, true);
+    if (st != MX_OK) return st;
+    HCK(cudaMemcpyAsync(y_host, h->y_stage, vb * (size_t)h->n_rows, cudaMemcpyDeviceToHost, h->stream));
+    HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+int mx_spmv_launches(mx_handle_t h) {
+    if (!h || !h->planned) return 0;
+    int n = resid_launches(h->resid);
+    if (h->stats.active) n += 1 + tile_launches(h->tile);
+    return n;
+}
+
+int mx_device_error(mx_handle_t h, int *err) {
+    if (!h || !err) return MX_ERR_INVALID;
+    HCK(cudaSetDevice(h->device));
+    HCK(cudaMemcpyAsync(err, h->dev_err, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile, float *ms_resid,
+                  float *ms_total) {
+    if (!h || !x_dev || !y_dev || warm < 0 || iters <= 0) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_timed: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    cudaEvent_t e0, e1;
+    HCK(cudaEventCreate(&e0));
+    HCK(cudaEventCreate(&e1));
+    float out[3] = {0, 0, 0};
+    for (int phase = 0; phase < 3; ++phase) {
+        const bool do_tile = phase != 1, do_resid = phase != 0;
+        if (phase == 0 && !h->stats.active) continue;
+        for (int i = 0; i < warm + iters; ++i) {
+            if (i == warm) HCK(cudaEventRecord(e0, h->stream));
+            int st;
+            if (phase == 2) {
+                st = spmv_enqueue(h, x_dev, y_dev, true, true);
+            } else if (h->stats.active) {
+                // one half alone, on an x that is already permuted (the reference times its halves the same way)
+                st = MX_OK;
+                if (i == 0) HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
+                if (do_tile)
+                    HCK(tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err,
+                                  h->stream));
+                if (do_resid)
+                    HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
+                                   h->stream));
+            } else {
+                st = spmv_enqueue(h, x_dev, y_dev, false, true);
+            }
+            if (st != MX_OK) return st;
+        }
+        HCK(cudaEventRecord(e1, h->stream));
+        HCK(cudaEventSynchronize(e1));
+        float ms = 0;
+        HCK(cudaEventElapsedTime(&ms, e0, e1));
+        out[phase] = ms / iters;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (ms_tile) *ms_tile = out[0];
+    if (ms_resid) *ms_resid = out[1];
+    if (ms_total) *ms_total = out[2];
+    return MX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Stateless mirrors of include/MatXtract.h.  Errors are reported as a status; the C++ shims turn a
+// non-zero status into the reference's behaviour (message + exit).
+// ---------------------------------------------------------------------------------------------------
+#define SCK(call)                                                                           \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess) {                                                            \
+            fprintf(stderr, "CUDA Error: %s at %s:%d\n", cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return MX_ERR_CUDA;                                                             \
+        }                                                                                   \
+    } while (0)
+
+
+int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColInd, const void *x, void *y,
+              int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv, double *pre_ms) {
+    if ((dtype != MX_FP64 && dtype != MX_FP16) || !csrRowPtr || !x || !y || rowA < 0 || colA < 0 || nnzA < 0 ||
+        (nnzA > 0 && (!csrVal || !csrColInd)))
+        return MX_ERR_INVALID;
+    int st = check_device();
+    if (st != MX_OK) return st;
+    const size_t vb = val_bytes(dtype);
+    DevBufs B;
+    int *d_ptr, *d_ind;
+    void *d_val, *d_x, *d_y, *d_scratch;
+    SCK(B.up(&d_ptr, csrRowPtr, sizeof(int) * ((size_t)rowA + 1)));
+    SCK(B.up(&d_ind, csrColInd, sizeof(int) * (size_t)nnzA));
+    SCK(B.up(&d_val, csrVal, vb * (size_t)nnzA));
+    SCK(B.up(&d_x, x, vb * (size_t)colA));
+    SCK(B.up(&d_y, y, vb * (size_t)rowA));
+    SCK(B.up(&d_scratch, nullptr, vb * (size_t)rowA));
+    ResidPlan P;
+    P.n_rows = rowA;
+    P.n_cols = colA;
+    P.nnz = nnzA;
+    P.row_ptr = d_ptr;
+    P.col_ind = d_ind;
+    P.val = d_val;
+    cudaEvent_t e0, e1;
+    SCK(cudaEventCreate(&e0));
+    SCK(cudaEventCreate(&e1));
+    SCK(cudaEventRecord(e0, 0));
+    cudaError_t ce = resid_plan_build(dtype, P, 0);
+    SCK(cudaEventRecord(e1, 0));
+    SCK(cudaEventSynchronize(e1));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (pre_ms) *pre_ms = ms;
+    if (ce == cudaSuccess) {
+        for (int i = 0; i < warm + iters && ce == cudaSuccess; ++i) {
+            if (i == warm) cudaEventRecord(e0, 0);
+            ce = resid_spmv(dtype, P, d_x, d_scratch, nullptr, nullptr, false, nullptr, 0);
+        }
+        cudaEventRecord(e1, 0);
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (ms_per_spmv) *ms_per_spmv = iters > 0 ? ms / iters : 0.0;
+        if (ce == cudaSuccess) ce = resid_spmv(dtype, P, d_x, d_y, nullptr, nullptr, true, nullptr, 0);  // y += A x
+        if (ce == cudaSuccess) ce = cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost);
+    }
+    resid_plan_free(P);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    SCK(ce);
+    return MX_OK;
+}
+
+static int run_tiles(int dtype, TileArrays &T, const void *d_x, void *d_y, void *d_scratch, int warm, int iters,
+                     bool accumulate, double *ms_per_spmv) {
+    TilePlan P;
+    P.A = T;
+    cudaError_t ce = tile_plan_build(dtype, P, 0);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    for (int i = 0; i < warm + iters && ce == cudaSuccess; ++i) {
+        if (i == warm) cudaEventRecord(e0, 0);
+        ce = tile_spmv(dtype, P, d_x, d_scratch, nullptr, false, false, nullptr, 0);
+    }
+    if (iters > 0 && ce == cudaSuccess) {
+        cudaEventRecord(e1, 0);
+        cudaEventSynchronize(e1);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (ms_per_spmv) *ms_per_spmv = ms / iters;
+    }
+    if (ce == cudaSuccess) ce = tile_spmv(dtype, P, d_x, d_y, nullptr, false, accumulate, nullptr, 0);
+    if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+    tile_plan_free(P);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    SCK(ce);
+    return MX_OK;
+}
+
+int mx_du_tcspmv(int dtype, const int *chunkPtr, const int *fragPtr, const void *fragBit, const void *tcVal,
+                 int n_vals, const int *AToX, const void *x, void *y, int dRows, int dCols, int warm, int iters,
+                 double *ms_per_spmv) {
+    if ((dtype != MX_FP64 && dtype != MX_FP16) || !chunkPtr || !fragPtr || !x || !y || dRows < 0 || dCols < 0 ||
+        n_vals < 0)
+        return MX_ERR_INVALID;
+    int st = check_device();
+    if (st != MX_OK) return st;
+    const size_t vb = val_bytes(dtype);
+    const int K = frag_k(dtype);
+    const int chunkNum = (dRows + 7) / 8;
+    const int totalFrags = chunkPtr[chunkNum];
+    if (totalFrags > 0 && (!fragBit || !AToX)) return MX_ERR_INVALID;
+    if (n_vals > 0 && !tcVal) return MX_ERR_INVALID;
+    DevBufs B;
+    TileArrays T;
+    T.dRows = dRows;
+    T.dCols = dCols;
+    T.chunkNum = chunkNum;
+    T.totalFrags = totalFrags;
+    T.nvals = n_vals;
+    void *d_x, *d_y, *d_scratch;
+    SCK(B.up(&T.chunkPtr, chunkPtr, sizeof(int) * ((size_t)chunkNum + 1)));
+    SCK(B.up(&T.fragPtr, fragPtr, sizeof(int) * ((size_t)totalFrags + 1)));
+    SCK(B.up(&T.fragBit, fragBit, bit_bytes(dtype) * (size_t)totalFrags));
+    SCK(B.up(&T.tcVal, tcVal, vb * (size_t)n_vals));
+    SCK(B.up(&T.AToX, AToX, sizeof(int) * (size_t)totalFrags * K));
+    SCK(B.up(&d_x, x, vb * (size_t)dCols));
+    SCK(B.up(&d_y, y, vb * (size_t)dRows));
+    SCK(B.up(&d_scratch, nullptr, vb * (size_t)dRows));
+    // FP64: the reference preloads y and adds to it; FP16: y is zeroed and stored
+    st = run_tiles(dtype, T, d_x, d_y, d_scratch, warm, iters, dtype == MX_FP64, ms_per_spmv);
+    if (st != MX_OK) return st;
+    SCK(cudaMemcpy(y, d_y, vb * (size_t)dRows, cudaMemcpyDeviceToHost));
+    return MX_OK;
+}
+
+int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColIdx, const void *x, void *y,
+                 int *order_rid, int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv) {
+    if ((dtype != MX_FP64 && dtype != MX_FP16) || !csrRowPtr || !x || !y || !order_rid || rowA < 0 || colA < 0 ||
+        nnzA < 0 || (nnzA > 0 && (!csrVal || !csrColIdx)))
+        return MX_ERR_INVALID;
+    int st = check_device();
+    if (st != MX_OK) return st;
+    const size_t vb = val_bytes(dtype);
+    DevBufs B;
+    int *d_ptr, *d_ind;
+    void *d_val, *d_x, *d_y, *d_scratch;
+    SCK(B.up(&d_ptr, csrRowPtr, sizeof(int) * ((size_t)rowA + 1)));
+    SCK(B.up(&d_ind, csrColIdx, sizeof(int) * (size_t)nnzA));
+    SCK(B.up(&d_val, csrVal, vb * (size_t)nnzA));
+    SCK(B.up(&d_x, x, vb * (size_t)colA));
+    SCK(B.up(&d_y, nullptr, vb * (size_t)rowA));
+    SCK(B.up(&d_scratch, nullptr, vb * (size_t)rowA));
+    TileArrays T;
+    int tstatus = MX_OK;
+    cudaError_t ce = tiles_from_dd(dtype, rowA, nnzA, d_ptr, d_ind, d_val, T, &tstatus, 0);
+    T.dCols = colA;
+    if (ce == cudaSuccess && tstatus == MX_OK) {
+        st = run_tiles(dtype, T, d_x, d_y, d_scratch, warm, iters, false, ms_per_spmv);
+        if (st == MX_OK && cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost) != cudaSuccess)
+            st = MX_ERR_CUDA;
+    } else {
+        st = ce != cudaSuccess ? MX_ERR_CUDA : tstatus;
+    }
+    tile_arrays_free(T);
+    for (int i = 0; i < rowA; ++i) order_rid[i] = i;
+    return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// Internal declarations shared by the translation units of libmatxtract_b200.so.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "mx_capi.h"
+
+namespace mx {
+
+// ------------------------------------------------------------------------------------------------
+// Residual CSR kernel geometry: a tile is RESID_THREADS * IPT consecutive non-zeros.
+constexpr int RESID_THREADS = 256;
+template <typename V>
+struct ResidCfg;
+template <>
+struct ResidCfg<double> {
+    static constexpr int IPT = 8;
+};
+template <>
+struct ResidCfg<__half> {
+    static constexpr int IPT = 16;
+};
+
+// Device error word bits.
+enum : int { DEVERR_RESID_SLICE = 1, DEVERR_TILE_RANGE = 2, DEVERR_PARTITION = 4 };
+
+// Plan + buffers of the residual CSR kernel for one CSR matrix that lives on the device.
+struct ResidPlan {
+    int n_rows = 0, n_cols = 0, nnz = 0;
+    const int *row_ptr = nullptr;  // [n_rows+1]
+    const int *col_ind = nullptr;  // [nnz]
+    const void *val = nullptr;     // [nnz]
+    int tile_nnz = 0, num_tiles = 0;
+    int *tile_row = nullptr;   // [num_tiles+1] rows whose end lies at or before the tile's first non-zero
+    void *carry = nullptr;     // [num_tiles] accumulate-type partial of the tile's unfinished last row
+    void *head = nullptr;      // [num_tiles] accumulate-type partial of a first row that began in an earlier tile
+};
+
+// Plain CSR on the device (non-owning view).
+struct CsrDev {
+    int n_rows = 0, n_cols = 0, nnz = 0;
+    const int *row_ptr = nullptr;
+    const int *col_ind = nullptr;
+    const void *val = nullptr;
+};
+
+// Tile-format matrix on the device (layout of the reference's fragment format).
+struct TileArrays {
+    int dRows = 0, dCols = 0, chunkNum = 0, totalFrags = 0, nvals = 0;
+    int *chunkPtr = nullptr;  // [chunkNum+1]
+    int *AToX = nullptr;      // [totalFrags*K]
+    int *fragPtr = nullptr;   // [totalFrags+1]
+    void *fragBit = nullptr;  // [totalFrags] uint32 / uint64
+    void *tcVal = nullptr;    // [nvals]
+};
+
+// Execution plan of the tile kernel over a TileArrays: a panel with many fragments is cut into several
+// work segments.
+struct TilePlan {
+    TileArrays A;  // view, not owned
+    int numSegs = 0, numMultiSegs = 0;
+    int *segPanel = nullptr;        // [numSegs]
+    int *segBegin = nullptr;        // [numSegs] fragment range of segment s = [segBegin[s], segEnd[s])
+    int *segEnd = nullptr;          // [numSegs]
+    int *segSlot = nullptr;         // [numSegs] slot in `partial` (-1: the panel has one segment, write directly)
+    int *panelFirstSeg = nullptr;   // [chunkNum+1]
+    void *partial = nullptr;        // [numMultiSegs][8] accumulate-type partial sums
+    unsigned *panelCount = nullptr; // [chunkNum] arrival counters of split panels (self-resetting)
+};
+
+// Everything the extraction produces, on the device (owned).
+struct PartArrays {
+    int *xperm = nullptr;        // [n_cols]
+    int *rId = nullptr;          // [dRows]
+    uint32_t *hotmask = nullptr; // [ceil(n_rows/32)] bit r set when row r is hot
+    int *rowPtr_dd = nullptr, *colInd_dd = nullptr;
+    void *val_dd = nullptr;
+    int *rowPtr_CD = nullptr, *colInd_CD = nullptr;
+    void *val_CD = nullptr;
+    TileArrays tiles;
+};
+
+// ---- launchers (each returns the cudaError_t of its launches) ----
+cudaError_t resid_plan_build(int dtype, ResidPlan &plan, cudaStream_t s);
+void resid_plan_free(ResidPlan &plan);
+// y[r] = sum_r (+ y_in[r] when accumulate) (+ ytile[r] for rows flagged in hotmask).  ytile is of the
+// accumulate type (float for FP16, double for FP64); hotmask has one bit per row.
+cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y, const void *ytile,
+                       const uint32_t *hotmask, bool accumulate, int *dev_err, cudaStream_t s);
+int resid_launches(const ResidPlan &plan);
+
+cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
+void tile_plan_free(TilePlan &plan);
+// out[row_map ? row_map[i] : i] (accumulate type when out_is_acc, else value type) = tile row i result.
+cudaError_t tile_spmv(int dtype, const TilePlan &plan, const void *x_d, void *out, const int *row_map,
+                      bool out_is_acc, bool accumulate, int *dev_err, cudaStream_t s);
+int tile_launches(const TilePlan &plan);
+
+cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st,
+                          int *status, cudaStream_t s);
+cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,
+                          const void *val_dd, TileArrays &T, int *status, cudaStream_t s);
+void part_arrays_free(PartArrays &P);
+void tile_arrays_free(TileArrays &T);
+
+// x_perm[i] = x[perm[i]]
+cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *x_perm, int n, cudaStream_t s);
+
+inline size_t val_bytes(int dtype) { return dtype == MX_FP64 ? 8 : 2; }
+inline size_t acc_bytes(int dtype) { return dtype == MX_FP64 ? 8 : 4; }
+inline int frag_k(int dtype) { return dtype == MX_FP64 ? 4 : 8; }
+inline size_t bit_bytes(int dtype) { return dtype == MX_FP64 ? 4 : 8; }
+
+}  // namespace mx
