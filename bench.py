@@ -1,0 +1,385 @@
+"""Benchmark of the MatXtract SpMV path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5|c1] [--n ROWS]
+
+One "step" is one SpMV y = A x of the workload matrix through the extraction's split execution (x permutation, tile
+kernel, residual CSR kernel).  The default workload is BASELINE.json's configs[1] (power-law graph, n = 2,000,000,
+FP16, tau = (0.46, 0.33)) generated from shape statistics (the reference's SuiteSparse inputs are not available
+offline).  With N > 1 (launched by torchrun, one rank per GPU) every rank owns an equal slab of rows of an
+(N*n) x (N*n) matrix of the same shape, x is replicated and y is all-gathered over NCCL inside the timed step: weak
+scaling.  Prints one JSON line (rank 0).
+
+--impl reference times the reference's serial CPU SpMV (its spmv_serial, from oracle/_ref when that was built from the
+reference sources, else the oracle port) on all host cores over row slabs of a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "spmv_gflops"
+UNIT = "GFLOP/s"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        super().__init__(daemon=True)
+        self.index, self.period, self.samples, self.reasons, self.max_mhz = index, period_s, [], set(), None
+        self.active = threading.Event()
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._halt.is_set():
+            if self.active.is_set():
+                try:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM))
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def workload_matrix(args, rank, world):
+    """This rank's slab of the (world*n) x (world*n) matrix, the full x, and the shape description."""
+    from matxtract_b200 import synth
+
+    cfg = synth.CONFIGS[args.workload]
+    n_local = args.n or cfg.n
+    n_total = n_local * world
+    m = synth.generate(cfg, n=n_total, rows=(rank * n_local, (rank + 1) * n_local))
+    return cfg, n_local, n_total, m
+
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def reference_spmv_callable(dtype):
+    """(fn(val, row_ptr_ptr, col, x, y, rows, cols, nnz) as a ctypes callable, kind)."""
+    import oracle
+
+    if oracle.ref_available():
+        return oracle.rlib(dtype).ref_spmv_serial, "reference"
+    L = oracle.olib()
+
+    def port(val, ptr, ind, x, y, rows, cols, nnz):
+        L.mxo_spmv_serial(dtype, val, ptr, ind, x, y, rows)
+
+    return port, "port"
+
+
+def cpu_spmv_time(dtype, m, rows, threads, repeats):
+    """Best-of-`repeats` seconds of the reference's serial SpMV over the first `rows` rows, split into `threads`
+    contiguous slabs of equal nnz (each slab is one call of the unmodified serial routine)."""
+    fn, kind = reference_spmv_callable(dtype)
+    rp = m["row_ptr"]
+    nnz = int(rp[rows])
+    bounds = [int(np.searchsorted(rp[: rows + 1], nnz * t // threads, side="left")) for t in range(threads)] + [rows]
+    bounds[0] = 0
+    vdt = np.float64 if dtype == 0 else np.float16
+    y = np.zeros(rows, vdt)
+    vp = ctypes.c_void_p
+    isz = 4
+
+    def slab(t):
+        a, b = bounds[t], bounds[t + 1]
+        if b <= a:
+            return
+        # the routine indexes val/col with the absolute row pointers, so only row_ptr and y are offset
+        fn(vp(m["val"].ctypes.data), vp(rp.ctypes.data + a * isz), vp(m["col_ind"].ctypes.data), vp(m["x"].ctypes.data),
+           vp(y.ctypes.data + a * y.itemsize), b - a, m["n"], nnz)
+
+    best = float("inf")
+    for _ in range(repeats):
+        y[:] = 0
+        ts = [threading.Thread(target=slab, args=(t,)) for t in range(threads)]
+        t0 = time.perf_counter()
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        best = min(best, time.perf_counter() - t0)
+    return best, nnz, kind
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg, n_local, n_total, m = workload_matrix(args, 0, 1)
+    dtype = m["dtype"]
+    threads = cpu_threads()
+    # bounded sample: calibrate on 50k rows, then size the sample so that all steps fit in ~100 s
+    probe_rows = min(n_local, 50_000)
+    t_probe, nnz_probe, kind = cpu_spmv_time(dtype, m, probe_rows, threads, 1)
+    rate = nnz_probe / max(t_probe, 1e-9)
+    budget_s = 100.0
+    want_nnz = rate * budget_s / max(1, args.steps + args.warmup)
+    rows = int(min(n_local, max(probe_rows, np.searchsorted(m["row_ptr"], want_nnz))))
+    for _ in range(args.warmup):
+        cpu_spmv_time(dtype, m, rows, threads, 1)
+    times = []
+    nnz = 0
+    for _ in range(args.steps):
+        t, nnz, kind = cpu_spmv_time(dtype, m, rows, threads, 1)
+        times.append(t)
+    ms = 1e3 * float(np.mean(times))
+    value = 2.0 * nnz / (ms * 1e-3) / 1e9
+    sample = f"first {rows} of {n_local} rows ({nnz} nnz), {threads} row slabs of the serial routine in parallel"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64" if dtype == 0 else "f16", "data": "synthetic",
+        "config": {"workload": describe(cfg, n_local, 1), "tau": list(cfg.tau)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def describe(cfg, n_local, world):
+    return (f"{cfg.name}: synthetic {['uniform', 'power-law', 'block 8x8', 'hot-column'][cfg.kind]} square CSR, "
+            f"{n_local} rows per GPU x {world} GPU(s), {'FP64' if cfg.dtype == 0 else 'FP16'}")
+
+
+def run_ours(args):
+    import torch
+
+    import matxtract_b200 as mx
+    from matxtract_b200 import synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+
+    cfg, n_local, n_total, m = workload_matrix(args, rank, world)
+    dtype = m["dtype"]
+    tdt = torch.float64 if dtype == mx.FP64 else torch.float16
+    tau = tuple(args.tau) if args.tau else cfg.tau
+
+    h = mx.MatXtract(dtype, device=local)
+    # this rank's slab: rows [rank*n_local, (rank+1)*n_local) x all n_total columns, extracted on its own
+    h.upload_csr(n_local, n_total, m["row_ptr"], m["col_ind"], m["val"])
+    st = h.partition(*tau)
+    stream = torch.cuda.ExternalStream(h.stream, device=torch.device("cuda", local))
+
+    x_host = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).pin_memory()
+    y_host = torch.empty(n_total, dtype=tdt).pin_memory()
+    with torch.cuda.stream(stream):
+        x_dev = x_host.to(f"cuda:{local}", non_blocking=True)
+        y_full = torch.zeros(n_total, dtype=tdt, device=f"cuda:{local}")
+        y_work = torch.zeros(n_local, dtype=tdt, device=f"cuda:{local}")
+    stream.synchronize()
+
+    def step_device():
+        if world == 1:
+            h.spmv(x_dev, y_full)
+        else:
+            h.spmv(x_dev, y_work)
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(y_full, y_work)
+
+    def step_e2e():
+        with torch.cuda.stream(stream):
+            x_dev.copy_(x_host, non_blocking=True)
+        step_device()
+        with torch.cuda.stream(stream):
+            y_host.copy_(y_full, non_blocking=True)
+        stream.synchronize()
+
+    def barrier():
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.active.set()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        sampler.active.clear()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=f"cuda:{local}", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    nnz_local = m["nnz"]
+    nnz_total = nnz_local
+    if dist is not None:
+        t = torch.tensor([nnz_local], device=f"cuda:{local}", dtype=torch.int64)
+        dist.all_reduce(t)
+        nnz_total = int(t.item())
+
+    ms_step = timed(step_device, args.steps, max(3, args.warmup))
+    value = 2.0 * nnz_total / (ms_step * 1e-3) / 1e9
+    ms_e2e = timed(step_e2e, max(10, args.steps // 10), 3)
+    e2e_value = 2.0 * nnz_total / (ms_e2e * 1e-3) / 1e9
+
+    # per-kernel timing (each half alone, CUDA events on the handle's stream) for the roofline of the dominant kernel
+    sampler.active.set()
+    halves = h.spmv_timed(x_dev, y_work, warm=max(3, args.warmup), iters=args.steps)
+    sampler.active.clear()
+    stream.synchronize()
+    sampler.stop()
+
+    vb = 8 if dtype == mx.FP64 else 2
+    n_rows_h = n_local
+    b_alg_total = synth.algorithmic_bytes(n_total, n_total, nnz_total, dtype)
+    # residual kernel: its own CSR + x + y; tile kernel: the original CSR bytes of the entries it covers + x_d + y_hot
+    b_resid = st.nnzCD * (vb + 4) + (n_rows_h + 1) * 4 + n_total * vb + n_rows_h * vb
+    b_tile = st.nnzRowD * (vb + 4) + (st.dRows + 1) * 4 + st.dCols * vb + st.dRows * vb
+    peak, peak_kind = measured_peaks()
+    if st.active and halves["ms_tile"] > halves["ms_resid"]:
+        dom, dom_ms, dom_bytes = "tile_kernel", halves["ms_tile"], b_tile
+    else:
+        dom, dom_ms, dom_bytes = "resid_kernel(+fixup)", halves["ms_resid"], b_resid
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # CPU baseline (rank 0, N = 1 only): the reference's serial CSR SpMV on one core, bounded sample
+    cpu = None
+    if world == 1:
+        probe = min(n_local, 100_000)
+        t_probe, nnz_probe, kind = cpu_spmv_time(dtype, m, probe, 1, 1)
+        rows = int(min(n_local, max(probe, np.searchsorted(m["row_ptr"], nnz_probe / max(t_probe, 1e-9) * 4.0))))
+        t_cpu, nnz_cpu, kind = cpu_spmv_time(dtype, m, rows, 1, 3)
+        cpu = {"value": 2.0 * nnz_cpu / t_cpu / 1e9, "unit": UNIT, "cores": 1, "kind": kind,
+               "sample": f"first {rows} of {n_local} rows ({nnz_cpu} nnz), serial, best of 3",
+               "host_threads_available": cpu_threads()}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64" if dtype == mx.FP64 else "f16", "data": "synthetic",
+        "config": {"workload": describe(cfg, n_local, world), "tau": list(tau), "n": n_total, "nnz": nnz_total,
+                   "l2": "no flush: the matrix streamed per step is larger than the 126 MB L2"
+                   if b_alg_total / world > 126e6 else "matrix smaller than L2: latency figure, not a bandwidth figure",
+                   "parallelism": f"rows x{world}, x replicated, y all-gather (NCCL)" if world > 1 else "1 GPU"},
+        "effective_gbs": eff_gbs, "pct_of_8tbs": 100.0 * eff_gbs / NOMINAL_HBM_GBS / world,
+        "pct_of_measured_hbm": 100.0 * eff_gbs / peak / world,
+        "algorithmic_bytes_per_step": b_alg_total,
+        "partition": {k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
+        "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms,
+        "ms_tile_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": n_total * vb,
+                "d2h_bytes_per_step": n_total * vb},
+        "gpu_launches": h.launches_per_spmv * args.steps,
+        "clocks": sampler.summary(),
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    h.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
+    ap.add_argument("--tau", type=float, nargs=2, default=None)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -18,7 +18,7 @@ extern "C" {
 
 enum {
     MX_OK = 0,
-    MX_ERR_INVALID = 1,  /* bad argument (null pointer, negative size, non-square matrix for a partition ...) */
+    MX_ERR_INVALID = 1,  /* bad argument (null pointer, negative size ...) */
     MX_ERR_CUDA = 2,     /* a CUDA runtime call failed; see mx_last_error_string */
     MX_ERR_TAU = 3,      /* tau_c < tau_r, or a threshold that no prefix of the ranking reaches */
     MX_ERR_STATE = 4,    /* call order: no matrix uploaded, no partition built ... */
@@ -66,7 +66,9 @@ typedef struct {
  * ranking inside the hot columns and tau_r hot-row selection, dense 8xK tile construction, residual CSR
  * compaction.  Replaces the host pipeline inside main() of test/test_autotc_spmv.cpp:1119-1421,1486-1492
  * and its three cuSPARSE transposes (utilities/csr2csc.cpp).  tau_c and tau_r are converted to float
- * exactly as the reference does (:1103-1104); tau_c < tau_r is rejected (:1064-1069) with MX_ERR_TAU. */
+ * exactly as the reference does (:1103-1104); tau_c < tau_r is rejected (:1064-1069) with MX_ERR_TAU.
+ * The reference assumes a square matrix; a rectangular row slab (rows < cols, one GPU's share of a
+ * row-partitioned matrix) is accepted as well and is extracted on its own. */
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats);
 int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats);
 

@@ -215,7 +215,9 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         h->stats.sRows = h->n_rows;
         h->stats.nnzColS = h->nnz;
     } else {
-        if (h->n_rows != h->n_cols) return h->fail(MX_ERR_INVALID, "mx_partition: the extraction needs a square matrix");
+        // The reference assumes a square matrix (its tau_c scan runs i < rowA over the column table,
+        // test/test_autotc_spmv.cpp:1133).  A rectangular row slab (one GPU's share of a row-partitioned
+        // matrix) is accepted too: the scan then runs over min(rows, cols) ranked columns.
         CsrDev A;
         A.n_rows = h->n_rows;
         A.n_cols = h->n_cols;

@@ -1,0 +1,230 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.  Bit-exact for every array of the partition;
+y within max|y - y_ref| / max_i(sum_j |a_ij||x_j|) <= 1e-12 (FP64) / 2e-3 (FP16)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import matxtract_b200 as mx
+import oracle
+from matxtract_b200 import FP16, FP64, synth
+
+from cases import TAUS, small_cases, values
+
+pytestmark = pytest.mark.gpu
+
+TOL = {FP64: 1e-12, FP16: 2e-3}
+CASES = small_cases()
+PART_KEYS = ("xperm", "rId", "rowPtr_dd", "colInd_dd", "val_dd", "chunkPtr", "AToX", "fragPtr", "fragBit", "tcVal",
+             "rowPtr_CD", "colInd_CD", "val_CD")
+STAT_KEYS = ("dCols", "nnzColD", "sCols", "nnzColS", "dRows", "nnzRowD", "sRows", "nnzRowS", "chunkNum", "totalFrags",
+             "nnzCD")
+
+
+def _bits(a):
+    return np.ascontiguousarray(a).view(np.uint8)
+
+
+def check_y(dtype, y, rp, ci, val, x):
+    """Against the reference's serial valT-arithmetic result with the task's tolerance, and against an exactly
+    accumulated product (the CUDA path accumulates FP16 in FP32, so it must be at least as close to that)."""
+    y_ref = oracle.spmv_serial(dtype, rp, ci, val, x)
+    err = oracle.y_error(dtype, y, y_ref, rp, ci, val, x)
+    assert err <= TOL[dtype], f"error vs reference arithmetic {err}"
+    exact = oracle.exact_spmv(rp, ci, val, x)
+    err_exact = oracle.y_error(dtype, y, exact, rp, ci, val, x)
+    assert err_exact <= (1e-13 if dtype == FP64 else 6e-4), f"error vs exact {err_exact}"
+    assert oracle.eqcheck(dtype, y_ref, y) == -1 or dtype == FP16  # the reference's own 1e-8 relative check (FP64)
+    return err
+
+
+def assert_partition_equal(dtype, h, o):
+    s = h.stats
+    for k in STAT_KEYS:
+        assert getattr(s, k) == o["stats"][k], k
+    assert s.tc_nnz_ratio == pytest.approx(o["stats"]["tc_nnz_ratio"], rel=0, abs=0) or s.totalFrags == 0
+    d = h.download_partition()
+    for k in PART_KEYS:
+        np.testing.assert_array_equal(_bits(d[k]), _bits(o[k]), err_msg=k)
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_residual_only_tau_zero(dtype, case):
+    name, n, rp, ci = case
+    val, x = values(dtype, len(ci), 1), values(dtype, n, 2)
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, val)
+    st = h.partition(0.0, 0.0)
+    assert st.active == 0 and st.nnzCD == len(ci)
+    y = h.spmv_host(x)
+    check_y(dtype, y, rp, ci, val, x)
+    y2 = h.spmv_host(x)
+    np.testing.assert_array_equal(_bits(y), _bits(y2))  # no float atomics: bit-reproducible
+    assert h.device_error() == 0
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+@pytest.mark.parametrize("tau", TAUS)
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_partition_bit_exact_and_split_spmv(dtype, tau, case):
+    name, n, rp, ci = case
+    val, x = values(dtype, len(ci), 3), values(dtype, n, 4)
+    try:
+        o = oracle.partition(dtype, n, n, rp, ci, val, *tau)
+    except oracle.OracleError as e:
+        h = mx.MatXtract(dtype)
+        h.upload_csr(n, n, rp, ci, val)
+        with pytest.raises(mx.MxError) as ge:
+            h.partition(*tau)
+        assert ge.value.status == e.status
+        return
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(*tau)
+    assert_partition_equal(dtype, h, o)
+    y = h.spmv_host(x)
+    check_y(dtype, y, rp, ci, val, x)
+    np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
+    assert h.device_error() == 0
+    h.close()
+
+
+GOLDEN = sorted((Path(__file__).parent / "golden").glob("*.npz"))
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[f.stem for f in GOLDEN])
+def test_gpu_partition_reproduces_reference_golden(path):
+    """Directly against the arrays the reference's own host code produced (no oracle in between)."""
+    g = np.load(path)
+    dtype, n = int(g["dtype"]), int(g["n"])
+    val, x = oracle.init_vec(dtype, len(g["col_ind"])), oracle.init_vec(dtype, n)
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, g["row_ptr"], g["col_ind"], val)
+    s = h.partition(*tuple(g["tau"]))
+    assert [s.dRows, s.dCols, s.nnzRowD] == list(g["ref_se_dims"])
+    d = h.download_partition()
+    for k in ("rowPtr_CD", "colInd_CD", "val_CD", "rowPtr_dd", "colInd_dd", "val_dd", "chunkPtr", "AToX", "fragPtr",
+              "fragBit", "tcVal"):
+        np.testing.assert_array_equal(_bits(g["ref_" + k]), _bits(d[k]), err_msg=k)
+    np.testing.assert_array_equal(_bits(g["ref_x_CD"]), _bits(x[d["xperm"]]))
+    y = h.spmv_host(x)
+    # values are small integers: FP64 sums are exact whatever the order, so y must equal the reference's bit for bit
+    if dtype == FP64:
+        np.testing.assert_array_equal(g["ref_y_final"], y)
+    else:
+        assert oracle.eqcheck(dtype, g["ref_y_final"], y) == -1
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_tau_c_below_tau_r_is_rejected(dtype):
+    name, n, rp, ci = CASES[0]
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, values(dtype, len(ci), 1))
+    for tc in (0.0, 0.25, 0.5):
+        for tr in (0.25, 0.5, 0.75):
+            if tc < tr:
+                with pytest.raises(mx.MxError) as e:
+                    h.partition(tc, tr)
+                assert e.value.status == 3
+    with pytest.raises(mx.MxError) as e:  # no plan after a rejected call
+        h.spmv_host(values(dtype, n, 2))
+    assert e.value.status == 4
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_edge_shapes(dtype):
+    vdt = np.float64 if dtype == FP64 else np.float16
+    # empty matrix, all-empty rows, a single dense row, one row longer than several tiles
+    h = mx.MatXtract(dtype)
+    n = 50
+    h.upload_csr(n, n, np.zeros(n + 1, np.int32), np.zeros(0, np.int32), np.zeros(0, vdt))
+    h.partition(0, 0)
+    np.testing.assert_array_equal(h.spmv_host(np.ones(n, vdt)), np.zeros(n, vdt))
+    n = 20000
+    rp = np.zeros(n + 1, np.int32)
+    rp[7:] = n  # row 6 holds every column, all other rows empty
+    ci = np.arange(n, dtype=np.int32)
+    val, x = values(dtype, n, 5), values(dtype, n, 6)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(0, 0)
+    check_y(dtype, h.spmv_host(x), rp, ci, val, x)
+    h.partition(0.5, 0.5)
+    check_y(dtype, h.spmv_host(x), rp, ci, val, x)
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_stateless_mirrors_of_the_reference_api(dtype):
+    name, n, rp, ci = CASES[2]
+    val, x = values(dtype, len(ci), 7), values(dtype, n, 8)
+    y0 = values(dtype, n, 9)
+    # cdspmv: y is in/out
+    y, ms, pre = mx.cdspmv(dtype, val, rp, ci, x, y0, warm=2, iters=3)
+    y_ref = oracle.spmv_serial(dtype, rp, ci, val, x, y0)
+    denom = oracle.abs_rowsum_max(dtype, rp, ci, val, x) + float(np.abs(y0.astype(np.float64)).max())
+    assert np.abs(y.astype(np.float64) - y_ref.astype(np.float64)).max() / denom <= TOL[dtype]
+    assert ms > 0
+    # du / se on the oracle's core-dense block
+    o = oracle.partition(dtype, n, n, rp, ci, val, 0.75, 0.5)
+    st = o["stats"]
+    x_d = x[o["xperm"][: st["dCols"]]]
+    want = oracle.exact_spmv(o["rowPtr_dd"], o["colInd_dd"], o["val_dd"], x_d)
+    scale = oracle.abs_rowsum_max(dtype, o["rowPtr_dd"], o["colInd_dd"], o["val_dd"], x_d)
+    y_du, _ = mx.du_tcspmv(dtype, o["chunkPtr"], o["fragPtr"], o["fragBit"], o["tcVal"], o["AToX"], x_d,
+                           np.zeros(st["dRows"]), st["dRows"], warm=1, iters=2)
+    assert np.abs(y_du.astype(np.float64) - want).max() / scale <= (1e-13 if dtype == FP64 else 6e-4)
+    y_se, order, _ = mx.se_tcspmv(dtype, o["val_dd"], o["rowPtr_dd"], o["colInd_dd"], x_d, warm=1, iters=2)
+    got = np.empty_like(y_se)
+    got[order] = y_se
+    assert np.abs(got.astype(np.float64) - want).max() / scale <= (1e-13 if dtype == FP64 else 6e-4)
+    if dtype == FP64:  # du adds into y (the reference preloads it)
+        y_du2, _ = mx.du_tcspmv(dtype, o["chunkPtr"], o["fragPtr"], o["fragBit"], o["tcVal"], o["AToX"], x_d,
+                                np.ones(st["dRows"]), st["dRows"])
+        np.testing.assert_allclose(y_du2, y_du + 1.0, rtol=0, atol=1e-12 * max(scale, 1))
+
+
+MEDIUM = [("c1", 10_000, (0.0, 0.0)), ("c2", 200_000, (0.46, 0.33)), ("c3", 8 * 30_000, (0.5, 0.5)),
+          ("c4", 300_000, (0.5, 0.25)), ("c4", 300_000, (0.75, 0.75)), ("c5", 400_000, (0.0, 0.0)),
+          ("c5", 400_000, (0.7, 0.5))]
+
+
+@pytest.mark.parametrize("name,n,tau", MEDIUM, ids=[f"{a}-{b}-{c}" for a, b, c in MEDIUM])
+def test_benchmark_shapes_at_reduced_size(name, n, tau):
+    m = synth.generate(name, n=n)
+    dtype, rp, ci, val, x = m["dtype"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(*tau)
+    if tau != (0.0, 0.0):
+        assert_partition_equal(dtype, h, oracle.partition(dtype, n, n, rp, ci, val, *tau))
+    y = h.spmv_host(x)
+    check_y(dtype, y, rp, ci, val, x)
+    np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
+    assert h.device_error() == 0
+    h.close()
+
+
+def test_c4_tau_sweep_valid_and_rejected_points():
+    m = synth.generate("c4", n=100_000)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(FP16)
+    h.upload_csr(n, n, rp, ci, val)
+    valid = rejected = 0
+    for tc in synth.C4_TAUS:
+        for tr in synth.C4_TAUS:
+            if tc < tr:
+                with pytest.raises(mx.MxError):
+                    h.partition(tc, tr)
+                rejected += 1
+                continue
+            h.partition(tc, tr)
+            if (tc, tr) != (0.0, 0.0):
+                assert_partition_equal(FP16, h, oracle.partition(FP16, n, n, rp, ci, val, tc, tr))
+            check_y(FP16, h.spmv_host(x), rp, ci, val, x)
+            valid += 1
+    assert (valid, rejected) == (10, 6)
+    h.close()
