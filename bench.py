@@ -232,6 +232,8 @@ def run_ours(args):
     # this rank's slab: rows [rank*n_local, (rank+1)*n_local) x all n_total columns, extracted on its own
     h.upload_csr(n_local, n_total, m["row_ptr"], m["col_ind"], m["val"])
     st = h.partition(*tau)
+    if args.dd != "auto":
+        h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR}[args.dd])
     stream = torch.cuda.ExternalStream(h.stream, device=torch.device("cuda", local))
 
     x_host = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).pin_memory()
@@ -313,20 +315,30 @@ def run_ours(args):
     b_tile = st.nnzRowD * (vb + 4) + (st.dRows + 1) * 4 + st.dCols * vb + st.dRows * vb
     peak, peak_kind = measured_peaks()
     if st.active and halves["ms_tile"] > halves["ms_resid"]:
-        dom, dom_ms, dom_bytes = "tile_kernel", halves["ms_tile"], b_tile
+        dom, dom_ms, dom_bytes = ("tile_kernel" if h.dd_executor == 1 else "resid_kernel on dd"), halves["ms_tile"], b_tile
     else:
         dom, dom_ms, dom_bytes = "resid_kernel(+fixup)", halves["ms_resid"], b_resid
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
 
-    if rank != 0:
+    def shutdown():
+        # torch tensors that lived on the handle's stream must go before the stream does
+        nonlocal x_dev, y_full, y_work, x_host, y_host
+        stream.synchronize()
+        del x_dev, y_full, y_work, x_host, y_host  # pinned buffers record events on the stream when freed
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        h.close()
         if dist is not None:
             dist.destroy_process_group()
+
+    if rank != 0:
+        shutdown()
         return
 
     # CPU baseline (rank 0, N = 1 only): the reference's serial CSR SpMV on one core, bounded sample
     cpu = None
-    if world == 1:
+    if world == 1 and not args.no_cpu_baseline:
         probe = min(n_local, 100_000)
         t_probe, nnz_probe, kind = cpu_spmv_time(dtype, m, probe, 1, 1)
         rows = int(min(n_local, max(probe, np.searchsorted(m["row_ptr"], nnz_probe / max(t_probe, 1e-9) * 4.0))))
@@ -347,6 +359,7 @@ def run_ours(args):
         "pct_of_measured_hbm": 100.0 * eff_gbs / peak / world,
         "algorithmic_bytes_per_step": b_alg_total,
         "partition": {k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
+        "dd_executor": {1: "tile (tensor cores)", 2: "csr (CUDA cores)"}.get(h.dd_executor, "none"),
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms,
         "ms_tile_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
@@ -360,9 +373,7 @@ def run_ours(args):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
-    h.close()
-    if dist is not None:
-        dist.destroy_process_group()
+    shutdown()
 
 
 def main():
@@ -374,6 +385,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
+    ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr"], help="executor of the core-dense block")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -104,6 +104,15 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
  * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */
 int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile,
                   float *ms_resid, float *ms_total);
+/* Executor of the core-dense block.  The reference switches between its "dense-unfold" fragment kernel and its
+ * "sparse-encode" kernel on nnz and the fragment fill ratio (test/test_autotc_spmv.cpp:1507,1518).  Here:
+ * MX_DD_TILE = the tensor-core fragment kernel, MX_DD_CSR = the CUDA-core CSR kernel on the same entries (the
+ * role of the sparse-encode path), MX_DD_AUTO = tile kernel when tc_nnz_ratio >= MX_DD_AUTO_FILL.  The partition
+ * arrays do not depend on the choice. */
+enum { MX_DD_AUTO = 0, MX_DD_TILE = 1, MX_DD_CSR = 2 };
+#define MX_DD_AUTO_FILL 0.25
+int mx_set_dd_executor(mx_handle_t h, int mode);
+int mx_dd_executor(mx_handle_t h); /* the one in use: MX_DD_TILE or MX_DD_CSR */
 /* Number of kernel launches one mx_spmv issues for the current matrix / partition. */
 int mx_spmv_launches(mx_handle_t h);
 /* Device error word of the last kernels (0 = none). */

@@ -7,6 +7,7 @@ from pathlib import Path
 import numpy as np
 
 FP64, FP16 = 0, 1
+DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
 
 STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
@@ -60,6 +61,8 @@ SYMBOLS = {
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_spmv_launches": (_i, [_vp]),
+    "mx_set_dd_executor": (_i, [_vp, _i]),
+    "mx_dd_executor": (_i, [_vp]),
     "mx_device_error": (_i, [_vp, _ip]),
     "mx_cdspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d), C.POINTER(_d)]),
     "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
@@ -180,6 +183,14 @@ class MatXtract:
         t, r, a = C.c_float(), C.c_float(), C.c_float()
         self._ck(lib().mx_spmv_timed(self._h, _ptr(x_dev), _ptr(y_dev), warm, iters, C.byref(t), C.byref(r), C.byref(a)))
         return {"ms_tile": t.value, "ms_resid": r.value, "ms_total": a.value}
+
+    def set_dd_executor(self, mode: int):
+        """0 = auto (by fill ratio), 1 = tensor-core tile kernel, 2 = CSR kernel on the core-dense block."""
+        self._ck(lib().mx_set_dd_executor(self._h, mode))
+
+    @property
+    def dd_executor(self) -> int:
+        return lib().mx_dd_executor(self._h)
 
     @property
     def stream(self) -> int:

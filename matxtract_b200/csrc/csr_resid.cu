@@ -3,12 +3,15 @@
 //
 // Work is split by non-zeros, not by rows: a tile is THREADS*IPT consecutive non-zeros, so a power-law
 // row of 100 000 entries and a thousand rows of 4 entries cost the same.  Per tile:
-//   A. every thread loads 4 consecutive column indices (one 128-bit load) and 4 values (64/2x128 bit),
-//      gathers x through the read-only path, and writes the products to shared memory;
-//   B. every thread then owns IPT consecutive products, walks the row ends that fall inside them and
-//      emits finished rows; sums of rows that cross threads are joined by a key-segmented scan over the
-//      tile (warp shuffles), so no atomics are used and the result is bit-reproducible;
-//   C. rows that cross tiles leave a "carry" (tile's unfinished last row) and a "head" (first row that
+//   A. every thread loads its own IPT consecutive column indices and values with 128-bit read-only loads
+//      (evict-first, so the stream does not displace x from L1), gathers x through the read-only path
+//      and keeps the IPT products in registers — no shared-memory transposition;
+//   B. it then walks the row ends that fall inside its products (the tile's slice of the row pointers
+//      sits in shared memory as 16-bit offsets) and drops finished row sums into shared memory; sums of
+//      rows that cross threads are joined by a key-segmented scan over the tile (warp shuffles), so no
+//      atomics are used and the result is bit-reproducible;
+//   C. a coalesced epilogue stores one row per thread (adding the tile-kernel contribution of hot rows);
+//   D. rows that cross tiles leave a "carry" (tile's unfinished last row) and a "head" (first row that
 //      began earlier); a second tiny kernel adds them in tile order.
 // Every row of y is stored exactly once; rows that also have a tile-kernel contribution (flagged in
 // `hotmask`) add it at that point, so there is no merge pass.
@@ -35,12 +38,12 @@ __device__ __forceinline__ double to_acc(double v) { return v; }
 __device__ __forceinline__ void from_acc(double a, double *o) { *o = a; }
 __device__ __forceinline__ void from_acc(float a, __half *o) { *o = __float2half_rn(a); }
 
-// 16 bytes of padding after every 16 products: a thread's IPT consecutive products are then read with
-// conflict-free 128-bit shared loads, and the 4 products written in phase A stay 16-byte aligned.
-template <typename A>
-__device__ __forceinline__ int pidx(int i) {
-    return i + (i >> 4) * (16 / (int)sizeof(A));
-}
+// How a finished row leaves the kernel.
+enum OutMode : int {
+    OUT_Y = 0,        // y[r] = sum (+ tile contribution of hot rows)
+    OUT_Y_ACCUM = 1,  // y[r] += sum  (the reference's cdspmv adds into y, cdSpMV.cu:418,483)
+    OUT_CARRIER = 2   // carrier[row_map[r]] = sum in the accumulate type (core-dense block run as CSR)
+};
 
 __global__ void tile_row_kernel(const int *__restrict__ rowPtr, int n_rows, int nnz, int tile_nnz, int num_tiles,
                                 int *__restrict__ tile_row) {
@@ -63,131 +66,124 @@ __global__ void tile_row_kernel(const int *__restrict__ rowPtr, int n_rows, int 
     tile_row[t] = lo;
 }
 
-template <typename V, bool HAS_TILE, bool ACCUM>
-__device__ __forceinline__ void store_row(V *__restrict__ y, int r, typename AccOf<V>::T v,
-                                          const typename AccOf<V>::T *__restrict__ ytile,
-                                          const uint32_t *__restrict__ hotmask) {
-    if (HAS_TILE) {
-        if ((__ldg(hotmask + (r >> 5)) >> (r & 31)) & 1u) v += ytile[r];
+template <typename V>
+struct RowOut {
+    using A = typename AccOf<V>::T;
+    V *__restrict__ y;
+    A *__restrict__ carrier_out;           // OUT_CARRIER
+    const int *__restrict__ row_map;       // OUT_CARRIER
+    const A *__restrict__ ytile;           // HAS_TILE: tile-half contribution per row
+    const uint32_t *__restrict__ hotmask;  // HAS_TILE: bit r set when row r has one
+};
+
+template <typename V, bool HAS_TILE, int MODE>
+__device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename AccOf<V>::T v) {
+    if (MODE == OUT_CARRIER) {
+        o.carrier_out[o.row_map[r]] = v;
+        return;
     }
-    if (ACCUM) v += to_acc(y[r]);
-    from_acc(v, y + r);
+    if (HAS_TILE) {
+        if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
+    }
+    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
+    from_acc(v, o.y + r);
 }
 
-template <typename V, int IPT, bool HAS_TILE, bool ACCUM>
+// 128-bit read-only loads that do not displace the gathered x from L1
+__device__ __forceinline__ int4 ldg_stream(const int4 *p) {
+    int4 r;
+    asm volatile("ld.global.nc.L1::evict_first.v4.s32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+template <typename V, int IPT, bool HAS_TILE, int MODE>
 __global__ void __launch_bounds__(RESID_THREADS)
     resid_kernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd, const V *__restrict__ val,
-                 const V *__restrict__ x, V *__restrict__ y, const typename AccOf<V>::T *__restrict__ ytile,
-                 const uint32_t *__restrict__ hotmask, const int *__restrict__ tileRow,
+                 const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
                  typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int n_rows,
                  int nnz) {
     using A = typename AccOf<V>::T;
     constexpr int THREADS = RESID_THREADS;
     constexpr int T = THREADS * IPT;
-    constexpr int SMAX = T + 8;
-    constexpr int PADW = 16 / (int)sizeof(A);
-    __shared__ __align__(16) A sp[T + (T / 16) * PADW];
-    __shared__ int sEnd[SMAX + 1];
+    constexpr int KMAX = T / 2;  // row ends a tile keeps in shared memory (more: slow path through global memory)
+    __shared__ unsigned short sEnd[KMAX + 2];
+    __shared__ A ysum[KMAX];
     __shared__ A warpVal[THREADS / 32];
     __shared__ int warpKey[THREADS / 32];
 
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int base = t * T;  // nnz < 2^31, so base fits
     const int cnt = min(T, nnz - base);
-    const int r0 = tileRow[t], rE = tileRow[t + 1];
-    const int nEmit = rE - r0;
-    const int ne = min(rE + 1, n_rows) - r0;  // row ends this tile may look at
-    const bool inSmem = ne <= SMAX;
-    if (inSmem) {
-        for (int k = tid; k < ne; k += THREADS) sEnd[k] = rowPtr[r0 + 1 + k] - base;
-        if (tid == 0) sEnd[ne] = INT_MAX;
-    }
-    const bool headOpen = (r0 < n_rows) && (rowPtr[r0] < base);
+    const int a = tid * IPT;
 
-    // ---- phase A: products, striped over the tile in groups of 4 ----
-    {
-        const int *cbase = colInd + base;
-        const V *vbase = val + base;
-        int4 c[IPT / 4];
-        A v[IPT / 4][4];
+    // ---- this thread's IPT consecutive column indices and values (blocked, 128-bit loads) ----
+    int c[IPT];
+    A v[IPT];
+    if (a + IPT <= cnt) {
+        const int4 *cp = reinterpret_cast<const int4 *>(colInd + base + a);
 #pragma unroll
-        for (int j = 0; j < IPT / 4; ++j) {
-            const int i = (tid + j * THREADS) * 4;
-            if (i + 3 < cnt) {
-                c[j] = __ldg(reinterpret_cast<const int4 *>(cbase + i));
-                if constexpr (sizeof(V) == 2) {
-                    uint2 raw = __ldg(reinterpret_cast<const uint2 *>(vbase + i));
-                    __half2 h01 = *reinterpret_cast<__half2 *>(&raw.x), h23 = *reinterpret_cast<__half2 *>(&raw.y);
-                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                    v[j][0] = f01.x;
-                    v[j][1] = f01.y;
-                    v[j][2] = f23.x;
-                    v[j][3] = f23.y;
-                } else {
-                    double2 d01 = __ldg(reinterpret_cast<const double2 *>(vbase + i));
-                    double2 d23 = __ldg(reinterpret_cast<const double2 *>(vbase + i + 2));
-                    v[j][0] = d01.x;
-                    v[j][1] = d01.y;
-                    v[j][2] = d23.x;
-                    v[j][3] = d23.y;
-                }
-            } else {
-                int cc[4];
+        for (int q = 0; q < IPT / 4; ++q) {
+            int4 cc = ldg_stream(cp + q);
+            c[4 * q] = cc.x;
+            c[4 * q + 1] = cc.y;
+            c[4 * q + 2] = cc.z;
+            c[4 * q + 3] = cc.w;
+        }
+        if constexpr (sizeof(V) == 2) {
+            const int4 *vp = reinterpret_cast<const int4 *>(val + base + a);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    bool ok = i + q < cnt;
-                    cc[q] = ok ? __ldg(cbase + i + q) : 0;
-                    v[j][q] = ok ? to_acc(vbase[i + q]) : A(0);
+            for (int q = 0; q < IPT / 8; ++q) {
+                int4 raw = ldg_stream(vp + q);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float2 f = __half22float2(h[u]);
+                    v[8 * q + 2 * u] = f.x;
+                    v[8 * q + 2 * u + 1] = f.y;
                 }
-                c[j] = make_int4(cc[0], cc[1], cc[2], cc[3]);
+            }
+        } else {
+            const int4 *vp = reinterpret_cast<const int4 *>(val + base + a);
+#pragma unroll
+            for (int q = 0; q < IPT / 2; ++q) {
+                int4 raw = ldg_stream(vp + q);
+                const double *d = reinterpret_cast<const double *>(&raw);
+                v[2 * q] = d[0];
+                v[2 * q + 1] = d[1];
             }
         }
+    } else {
 #pragma unroll
-        for (int j = 0; j < IPT / 4; ++j) {
-            const int i = (tid + j * THREADS) * 4;
-            // entries past the end of the matrix have value 0 and column 0: harmless
-            A p0 = v[j][0] * to_acc(__ldg(x + c[j].x));
-            A p1 = v[j][1] * to_acc(__ldg(x + c[j].y));
-            A p2 = v[j][2] * to_acc(__ldg(x + c[j].z));
-            A p3 = v[j][3] * to_acc(__ldg(x + c[j].w));
-            A *dst = sp + pidx<A>(i);
-            if constexpr (sizeof(A) == 4) {
-                *reinterpret_cast<float4 *>(dst) = make_float4(p0, p1, p2, p3);
-            } else {
-                *reinterpret_cast<double2 *>(dst) = make_double2(p0, p1);
-                *reinterpret_cast<double2 *>(dst + 2) = make_double2(p2, p3);
-            }
+        for (int j = 0; j < IPT; ++j) {
+            const bool ok = a + j < cnt;
+            c[j] = ok ? __ldg(colInd + base + a + j) : 0;
+            v[j] = ok ? to_acc(val[base + a + j]) : A(0);  // past the end: value 0, column 0 (harmless)
         }
     }
+
+    // ---- rows this tile looks at ----
+    const int r0 = tileRow[t], rE = tileRow[t + 1];
+    const int nEmit = rE - r0;                // rows that end inside this tile
+    const int ne = min(rE + 1, n_rows) - r0;  // row ends the walk may compare against
+    const bool inSmem = ne <= KMAX;
+    if (inSmem) {
+        for (int k = tid; k < ne; k += THREADS) sEnd[k] = (unsigned short)min(rowPtr[r0 + 1 + k] - base, 0xFFFF);
+        if (tid == 0) sEnd[ne] = 0xFFFF;
+    }
+    const bool headOpen = (r0 < n_rows) && (rowPtr[r0] < base);  // first row began in an earlier tile
+
+    // ---- products ----
+    A p[IPT];
+#pragma unroll
+    for (int j = 0; j < IPT; ++j) p[j] = v[j] * to_acc(__ldg(x + c[j]));
     __syncthreads();
 
-    // ---- phase B: each thread owns IPT consecutive products ----
     auto rowEnd = [&](int k) -> int {
         if (inSmem) return sEnd[k];
         return k < ne ? rowPtr[r0 + 1 + k] - base : INT_MAX;
     };
-    const int a = tid * IPT;
-    A p[IPT];
-    {
-        const A *src = sp + pidx<A>(a);  // IPT <= 16: the chunk never crosses a padding slot
-        if constexpr (sizeof(A) == 4) {
-#pragma unroll
-            for (int q = 0; q < IPT / 4; ++q) {
-                float4 f = *reinterpret_cast<const float4 *>(src + 4 * q);
-                p[4 * q] = f.x;
-                p[4 * q + 1] = f.y;
-                p[4 * q + 2] = f.z;
-                p[4 * q + 3] = f.w;
-            }
-        } else {
-#pragma unroll
-            for (int q = 0; q < IPT / 2; ++q) {
-                double2 d = *reinterpret_cast<const double2 *>(src + 2 * q);
-                p[2 * q] = d.x;
-                p[2 * q + 1] = d.y;
-            }
-        }
-    }
     int k = 0;  // row (relative to r0) the thread's first product belongs to
     if (tid != 0) {
         int lo = 0, hi = ne;
@@ -204,11 +200,13 @@ __global__ void __launch_bounds__(RESID_THREADS)
     int headK = -1;
     int e = rowEnd(k);
     auto emit = [&]() {
-        if (headK < 0) {
+        if (headK < 0) {  // first row this thread finishes: it may have begun in an earlier thread
             headK = k;
             headAcc = acc;
+        } else if (inSmem) {
+            ysum[k] = acc;
         } else {
-            store_row<V, HAS_TILE, ACCUM>(y, r0 + k, acc, ytile, hotmask);
+            store_row<V, HAS_TILE, MODE>(out, r0 + k, acc);
         }
         acc = A(0);
         ++k;
@@ -226,16 +224,16 @@ __global__ void __launch_bounds__(RESID_THREADS)
 
     // ---- key-segmented inclusive scan of the (row, partial) tails over the tile ----
     int key = k;
-    A v = acc;
+    A sv = acc;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
         int k2 = __shfl_up_sync(0xffffffffu, key, d);
-        A v2 = __shfl_up_sync(0xffffffffu, v, d);
-        if (lane >= d && k2 == key) v += v2;
+        A v2 = __shfl_up_sync(0xffffffffu, sv, d);
+        if (lane >= d && k2 == key) sv += v2;
     }
     if (lane == 31) {
         warpKey[w] = key;
-        warpVal[w] = v;
+        warpVal[w] = sv;
     }
     __syncthreads();
     int ck = -1;  // carry into this warp
@@ -246,7 +244,7 @@ __global__ void __launch_bounds__(RESID_THREADS)
             if (warpKey[u] == ck) cv += warpVal[u];
     }
     int pk = __shfl_up_sync(0xffffffffu, key, 1);
-    A pv = __shfl_up_sync(0xffffffffu, v, 1);
+    A pv = __shfl_up_sync(0xffffffffu, sv, 1);
     if (lane == 0) {
         pk = ck;
         pv = cv;
@@ -256,18 +254,22 @@ __global__ void __launch_bounds__(RESID_THREADS)
     if (headK >= 0) {
         A hv = headAcc + (pk == headK ? pv : A(0));
         if (headK == 0 && headOpen)
-            head[t] = hv;  // the row began in an earlier tile: the fix-up kernel finishes it
+            head[t] = hv;  // the fix-up kernel finishes rows that span tiles
+        else if (inSmem)
+            ysum[headK] = hv;
         else
-            store_row<V, HAS_TILE, ACCUM>(y, r0 + headK, hv, ytile, hotmask);
+            store_row<V, HAS_TILE, MODE>(out, r0 + headK, hv);
     }
-    if (tid == THREADS - 1) carry[t] = v + (key == ck ? cv : A(0));
+    if (tid == THREADS - 1) carry[t] = sv + (key == ck ? cv : A(0));
+    if (!inSmem) return;  // block-uniform
+    __syncthreads();
+    // ---- coalesced epilogue: one row per thread per pass ----
+    for (int q = tid + (headOpen ? 1 : 0); q < nEmit; q += THREADS) store_row<V, HAS_TILE, MODE>(out, r0 + q, ysum[q]);
 }
 
 // Rows that span tiles: sum the carries of the tiles the row passed through, in tile order, then the head.
-template <typename V, int IPT, bool HAS_TILE, bool ACCUM>
-__global__ void resid_fixup_kernel(const int *__restrict__ rowPtr, V *__restrict__ y,
-                                   const typename AccOf<V>::T *__restrict__ ytile,
-                                   const uint32_t *__restrict__ hotmask, const int *__restrict__ tileRow,
+template <typename V, int IPT, bool HAS_TILE, int MODE>
+__global__ void resid_fixup_kernel(const int *__restrict__ rowPtr, RowOut<V> out, const int *__restrict__ tileRow,
                                    const typename AccOf<V>::T *__restrict__ carry,
                                    const typename AccOf<V>::T *__restrict__ head, int n_rows, int num_tiles) {
     using A = typename AccOf<V>::T;
@@ -281,7 +283,7 @@ __global__ void resid_fixup_kernel(const int *__restrict__ rowPtr, V *__restrict
     A s = A(0);
     for (int u = start / T; u < t; ++u) s += carry[u];
     s += head[t];
-    store_row<V, HAS_TILE, ACCUM>(y, r0, s, ytile, hotmask);
+    store_row<V, HAS_TILE, MODE>(out, r0, s);
 }
 
 template <typename V>
@@ -292,33 +294,38 @@ __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ p
 
 template <typename V>
 cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void *ytile, const uint32_t *hotmask,
-                         bool accumulate, cudaStream_t s) {
+                         int mode, const int *row_map, cudaStream_t s) {
     using A = typename AccOf<V>::T;
     constexpr int IPT = ResidCfg<V>::IPT;
-    const bool hasTile = ytile != nullptr && hotmask != nullptr;
+    const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
+    RowOut<V> out;
+    out.y = (V *)y;
+    out.carrier_out = (A *)y;
+    out.row_map = row_map;
+    out.ytile = (const A *)ytile;
+    out.hotmask = hotmask;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     int fgrid = (P.num_tiles - 1 + 127) / 128;
-#define MX_LAUNCH(HT, AC)                                                                                         \
-    do {                                                                                                          \
-        resid_kernel<V, IPT, HT, AC><<<grid, block, 0, s>>>(P.row_ptr, P.col_ind, (const V *)P.val, (const V *)x, \
-                                                            (V *)y, (const A *)ytile, hotmask, P.tile_row,       \
-                                                            (A *)P.carry, (A *)P.head, P.n_rows, P.nnz);         \
-        if (fgrid > 0)                                                                                            \
-            resid_fixup_kernel<V, IPT, HT, AC><<<fgrid, 128, 0, s>>>(P.row_ptr, (V *)y, (const A *)ytile,        \
-                                                                     hotmask, P.tile_row, (const A *)P.carry,   \
-                                                                     (const A *)P.head, P.n_rows, P.num_tiles); \
+#define MX_LAUNCH(HT, MD)                                                                                          \
+    do {                                                                                                           \
+        resid_kernel<V, IPT, HT, MD><<<grid, block, 0, s>>>(P.row_ptr, P.col_ind, (const V *)P.val, (const V *)x,  \
+                                                            out, P.tile_row, (A *)P.carry, (A *)P.head, P.n_rows,  \
+                                                            P.nnz);                                                \
+        if (fgrid > 0)                                                                                             \
+            resid_fixup_kernel<V, IPT, HT, MD><<<fgrid, 128, 0, s>>>(P.row_ptr, out, P.tile_row,                   \
+                                                                     (const A *)P.carry, (const A *)P.head,       \
+                                                                     P.n_rows, P.num_tiles);                      \
     } while (0)
-    if (hasTile) {
-        if (accumulate)
-            MX_LAUNCH(true, true);
-        else
-            MX_LAUNCH(true, false);
-    } else {
-        if (accumulate)
-            MX_LAUNCH(false, true);
-        else
-            MX_LAUNCH(false, false);
-    }
+    if (mode == OUT_CARRIER)
+        MX_LAUNCH(false, OUT_CARRIER);
+    else if (hasTile && mode == OUT_Y_ACCUM)
+        MX_LAUNCH(true, OUT_Y_ACCUM);
+    else if (hasTile)
+        MX_LAUNCH(true, OUT_Y);
+    else if (mode == OUT_Y_ACCUM)
+        MX_LAUNCH(false, OUT_Y_ACCUM);
+    else
+        MX_LAUNCH(false, OUT_Y);
 #undef MX_LAUNCH
     return cudaGetLastError();
 }
@@ -349,8 +356,15 @@ int resid_launches(const ResidPlan &P) { return P.num_tiles > 1 ? 2 : 1; }
 
 cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, const void *ytile,
                        const uint32_t *hotmask, bool accumulate, int *, cudaStream_t s) {
-    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, accumulate, s);
-    return resid_spmv_t<__half>(P, x, y, ytile, hotmask, accumulate, s);
+    const int mode = accumulate ? OUT_Y_ACCUM : OUT_Y;
+    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, mode, nullptr, s);
+    return resid_spmv_t<__half>(P, x, y, ytile, hotmask, mode, nullptr, s);
+}
+
+cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, void *carrier, const int *row_map,
+                                  cudaStream_t s) {
+    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
+    return resid_spmv_t<__half>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
 }
 
 cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *out, int n, cudaStream_t s) {

@@ -23,6 +23,9 @@ struct mx_handle_s {
     PartArrays part;
     ResidPlan resid;
     TilePlan tile;
+    ResidPlan ddcsr;         // the core-dense block as CSR, for the low-fill executor
+    int dd_mode = MX_DD_AUTO;
+    bool dd_use_tile = true;
     void *ytile = nullptr;   // [n_rows] accumulate-type carrier of the tile half
     void *x_perm = nullptr;  // [n_cols] x in partition order
     // staging for the host-pointer entry point
@@ -49,6 +52,7 @@ namespace {
 
 void drop_plan(mx_handle_t h) {
     resid_plan_free(h->resid);
+    resid_plan_free(h->ddcsr);
     tile_plan_free(h->tile);
     part_arrays_free(h->part);
     cudaFree(h->ytile);
@@ -245,6 +249,15 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         HCK(resid_plan_build(h->dtype, h->resid, h->stream));
         h->tile.A = h->part.tiles;
         HCK(tile_plan_build(h->dtype, h->tile, h->stream));
+        h->ddcsr.n_rows = h->stats.dRows;
+        h->ddcsr.n_cols = h->stats.dCols;
+        h->ddcsr.nnz = h->stats.nnzRowD;
+        h->ddcsr.row_ptr = h->part.rowPtr_dd;
+        h->ddcsr.col_ind = h->part.colInd_dd;
+        h->ddcsr.val = h->part.val_dd;
+        HCK(resid_plan_build(h->dtype, h->ddcsr, h->stream));
+        h->dd_use_tile = h->dd_mode == MX_DD_TILE ||
+                         (h->dd_mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
         HCK(cudaMalloc(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows));
         HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
         HCK(cudaMalloc(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols));
@@ -297,11 +310,17 @@ int mx_download_partition(mx_handle_t h, const mx_partition_arrays *o) {
     return MX_OK;
 }
 
+// the core-dense block: tensor-core tile kernel, or (low fill) the CSR kernel on the same entries
+static cudaError_t dd_enqueue(mx_handle_t h) {
+    if (h->dd_use_tile)
+        return tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err, h->stream);
+    return resid_spmv_to_carrier(h->dtype, h->ddcsr, h->x_perm, h->ytile, h->part.rId, h->stream);
+}
+
 static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid) {
     if (h->stats.active) {
         HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
-        if (do_tile)
-            HCK(tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err, h->stream));
+        if (do_tile) HCK(dd_enqueue(h));
         if (do_resid)
             HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
                            h->stream));
@@ -334,8 +353,21 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
 int mx_spmv_launches(mx_handle_t h) {
     if (!h || !h->planned) return 0;
     int n = resid_launches(h->resid);
-    if (h->stats.active) n += 1 + tile_launches(h->tile);
+    if (h->stats.active) n += 1 + (h->dd_use_tile ? tile_launches(h->tile) : resid_launches(h->ddcsr));
     return n;
+}
+
+int mx_set_dd_executor(mx_handle_t h, int mode) {
+    if (!h || mode < MX_DD_AUTO || mode > MX_DD_CSR) return MX_ERR_INVALID;
+    h->dd_mode = mode;
+    if (h->planned && h->stats.active)
+        h->dd_use_tile = mode == MX_DD_TILE || (mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
+    return MX_OK;
+}
+
+int mx_dd_executor(mx_handle_t h) {
+    if (!h || !h->planned || !h->stats.active) return MX_DD_AUTO;
+    return h->dd_use_tile ? MX_DD_TILE : MX_DD_CSR;
 }
 
 int mx_device_error(mx_handle_t h, int *err) {
@@ -367,9 +399,7 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
                 // one half alone, on an x that is already permuted (the reference times its halves the same way)
                 st = MX_OK;
                 if (i == 0) HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
-                if (do_tile)
-                    HCK(tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err,
-                                  h->stream));
+                if (do_tile) HCK(dd_enqueue(h));
                 if (do_resid)
                     HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
                                    h->stream));

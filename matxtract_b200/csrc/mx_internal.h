@@ -90,6 +90,9 @@ void resid_plan_free(ResidPlan &plan);
 // accumulate type (float for FP16, double for FP64); hotmask has one bit per row.
 cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y, const void *ytile,
                        const uint32_t *hotmask, bool accumulate, int *dev_err, cudaStream_t s);
+// carrier[row_map[r]] = sum_r in the accumulate type: runs the core-dense block as CSR (low-fill dispatch)
+cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &plan, const void *x, void *carrier, const int *row_map,
+                                  cudaStream_t s);
 int resid_launches(const ResidPlan &plan);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
