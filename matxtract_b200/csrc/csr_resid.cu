@@ -3,13 +3,17 @@
 //
 // Work is split by non-zeros, not by rows: a tile is THREADS*IPT consecutive non-zeros, so a power-law
 // row of 100 000 entries and a thousand rows of 4 entries cost the same.  Per tile:
-//   A. every thread loads its own IPT consecutive column indices and values with 128-bit read-only loads
-//      (evict-first, so the stream does not displace x from L1), gathers x through the read-only path
-//      and keeps the IPT products in registers — no shared-memory transposition;
-//   B. it then walks the row ends that fall inside its products (the tile's slice of the row pointers
-//      sits in shared memory as 16-bit offsets) and drops finished row sums into shared memory; sums of
-//      rows that cross threads are joined by a key-segmented scan over the tile (warp shuffles), so no
-//      atomics are used and the result is bit-reproducible;
+//   A. lane i of a warp takes non-zero i: column indices and values stream in with coalesced read-only
+//      loads (evict-first, so the stream does not displace x from L1) and the x gathers coalesce wherever
+//      consecutive non-zeros have consecutive columns (blocked / banded matrices); the products go to a
+//      padded shared-memory buffer;
+//   B. every thread then owns IPT consecutive products (conflict-free 128-bit shared loads).  The rows that
+//      end inside the tile have set one bit each in a shared-memory mask, and recorded the lowest row
+//      index per 32-non-zero word (rows without entries are taken out of the row space at plan time, so
+//      ends are distinct): a thread reads the IPT bits over its products, knows which row its first bit
+//      closes, and a branch-free walk drops finished row sums into shared memory.  What is left after a
+//      thread's last closed row is joined to the next closing thread by a flag-segmented warp-shuffle
+//      scan — no float atomics, so the result is bit-reproducible;
 //   C. a coalesced epilogue stores one row per thread (adding the tile-kernel contribution of hot rows);
 //   D. rows that cross tiles leave a "carry" (tile's unfinished last row) and a "head" (first row that
 //      began earlier); a second tiny kernel adds them in tile order.
@@ -17,6 +21,7 @@
 // `hotmask`) add it at that point, so there is no merge pass.
 #include <climits>
 
+#include "device_prims.cuh"
 #include "mx_internal.h"
 
 namespace mx {
@@ -45,25 +50,41 @@ enum OutMode : int {
     OUT_CARRIER = 2   // carrier[row_map[r]] = sum in the accumulate type (core-dense block run as CSR)
 };
 
-__global__ void tile_row_kernel(const int *__restrict__ rowPtr, int n_rows, int nnz, int tile_nnz, int num_tiles,
+// tile_row[t] = number of (non-empty) rows whose end lies at or before the first non-zero of tile t
+__global__ void tile_row_kernel(const int *__restrict__ cPtr, int m_rows, int nnz, int tile_nnz, int num_tiles,
                                 int *__restrict__ tile_row) {
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t > num_tiles) return;
-    if (t == 0) {
-        tile_row[0] = 0;
-        return;
-    }
     long long p = (long long)t * tile_nnz;
     if (p > nnz) p = nnz;
-    int lo = 0, hi = n_rows;  // number of rows whose end is <= p
+    int lo = 0, hi = m_rows;
     while (lo < hi) {
         int mid = (lo + hi) >> 1;
-        if (rowPtr[mid + 1] <= p)
+        if (cPtr[mid + 1] <= p)
             lo = mid + 1;
         else
             hi = mid;
     }
     tile_row[t] = lo;
+}
+
+// Empty rows are taken out of the kernel's row space once, at plan time.
+__global__ void nonempty_flag_kernel(const int *__restrict__ rowPtr, int n_rows, int *__restrict__ flag) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r <= n_rows) flag[r] = r < n_rows ? (rowPtr[r + 1] > rowPtr[r]) : 0;
+}
+__global__ void compress_rows_kernel(const int *__restrict__ rowPtr, const int *__restrict__ pos, int n_rows,
+                                     int *__restrict__ cPtr, int *__restrict__ nzRow, int *__restrict__ emptyRow) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const int k = pos[r];  // non-empty rows before r
+    if (rowPtr[r + 1] > rowPtr[r]) {
+        nzRow[k] = r;
+        cPtr[k + 1] = rowPtr[r + 1];
+    } else {
+        emptyRow[r - k] = r;
+    }
+    if (r == 0) cPtr[0] = 0;
 }
 
 template <typename V>
@@ -74,6 +95,7 @@ struct RowOut {
     const int *__restrict__ row_map;       // OUT_CARRIER
     const A *__restrict__ ytile;           // HAS_TILE: tile-half contribution per row
     const uint32_t *__restrict__ hotmask;  // HAS_TILE: bit r set when row r has one
+    const int *__restrict__ nzRow;         // k-th non-empty row -> row index (null: no empty rows, identity)
 };
 
 template <typename V, bool HAS_TILE, int MODE>
@@ -89,201 +111,187 @@ __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename Ac
     from_acc(v, o.y + r);
 }
 
-// 128-bit read-only loads that do not displace the gathered x from L1
-__device__ __forceinline__ int4 ldg_stream(const int4 *p) {
-    int4 r;
-    asm volatile("ld.global.nc.L1::evict_first.v4.s32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
+// read-only loads that do not displace the gathered x from L1
+__device__ __forceinline__ int ldg_stream(const int *p) {
+    int r;
+    asm volatile("ld.global.nc.L1::evict_first.s32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ float ldg_stream_val(const __half *p) {
+    unsigned short r;
+    asm volatile("ld.global.nc.L1::evict_first.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return __half2float(__ushort_as_half(r));
+}
+__device__ __forceinline__ double ldg_stream_val(const double *p) {
+    double r;
+    asm volatile("ld.global.nc.L1::evict_first.f64 %0, [%1];" : "=d"(r) : "l"(p));
     return r;
 }
 
+// 16 bytes of padding after every 16 products: the striped stores of phase A and the 128-bit blocked
+// loads of phase B are then both free of bank conflicts.
+template <typename A>
+__device__ __forceinline__ int pidx(int i) {
+    return i + (i >> 4) * (16 / (int)sizeof(A));
+}
+
 template <typename V, int IPT, bool HAS_TILE, int MODE>
-__global__ void __launch_bounds__(RESID_THREADS)
-    resid_kernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd, const V *__restrict__ val,
+__global__ void __launch_bounds__(RESID_THREADS, 4)
+    resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
                  const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
-                 typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int n_rows,
-                 int nnz) {
+                 typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz) {
     using A = typename AccOf<V>::T;
     constexpr int THREADS = RESID_THREADS;
     constexpr int T = THREADS * IPT;
-    constexpr int KMAX = T / 2;  // row ends a tile keeps in shared memory (more: slow path through global memory)
-    __shared__ unsigned short sEnd[KMAX + 2];
-    __shared__ A ysum[KMAX];
-    __shared__ A warpVal[THREADS / 32];
-    __shared__ int warpKey[THREADS / 32];
+    constexpr int NW = THREADS / 32;
+    constexpr int PADW = 16 / (int)sizeof(A);
+    __shared__ __align__(16) A sp[T + (T / 16) * PADW];  // products, padded
+    __shared__ A ysum[T];                                // sums of the rows that end in this tile
+    __shared__ unsigned sFlag[T / 32];                   // bit i set: a row ends after the tile's i-th non-zero
+    __shared__ int sFirst[T / 32];                       // lowest row (relative) that ends inside the 32-nnz word
+    __shared__ A warpTail[NW];
+    __shared__ int warpOpen[NW];
 
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int base = t * T;  // nnz < 2^31, so base fits
     const int cnt = min(T, nnz - base);
-    const int a = tid * IPT;
 
-    // ---- this thread's IPT consecutive column indices and values (blocked, 128-bit loads) ----
+    // ---- phase A: lane <-> consecutive non-zeros: coalesced streams, and gathers that coalesce on runs of
+    //      consecutive columns ----
     int c[IPT];
     A v[IPT];
-    if (a + IPT <= cnt) {
-        const int4 *cp = reinterpret_cast<const int4 *>(colInd + base + a);
+    const int *cb = colInd + base + tid;
+    const V *vb = val + base + tid;
+    if (cnt == T) {
 #pragma unroll
-        for (int q = 0; q < IPT / 4; ++q) {
-            int4 cc = ldg_stream(cp + q);
-            c[4 * q] = cc.x;
-            c[4 * q + 1] = cc.y;
-            c[4 * q + 2] = cc.z;
-            c[4 * q + 3] = cc.w;
-        }
-        if constexpr (sizeof(V) == 2) {
-            const int4 *vp = reinterpret_cast<const int4 *>(val + base + a);
-#pragma unroll
-            for (int q = 0; q < IPT / 8; ++q) {
-                int4 raw = ldg_stream(vp + q);
-                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    float2 f = __half22float2(h[u]);
-                    v[8 * q + 2 * u] = f.x;
-                    v[8 * q + 2 * u + 1] = f.y;
-                }
-            }
-        } else {
-            const int4 *vp = reinterpret_cast<const int4 *>(val + base + a);
-#pragma unroll
-            for (int q = 0; q < IPT / 2; ++q) {
-                int4 raw = ldg_stream(vp + q);
-                const double *d = reinterpret_cast<const double *>(&raw);
-                v[2 * q] = d[0];
-                v[2 * q + 1] = d[1];
-            }
+        for (int j = 0; j < IPT; ++j) {
+            c[j] = ldg_stream(cb + j * THREADS);
+            v[j] = ldg_stream_val(vb + j * THREADS);
         }
     } else {
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
-            const bool ok = a + j < cnt;
-            c[j] = ok ? __ldg(colInd + base + a + j) : 0;
-            v[j] = ok ? to_acc(val[base + a + j]) : A(0);  // past the end: value 0, column 0 (harmless)
+            const bool ok = tid + j * THREADS < cnt;
+            c[j] = ok ? ldg_stream(cb + j * THREADS) : 0;
+            v[j] = ok ? ldg_stream_val(vb + j * THREADS) : A(0);  // past the end: value 0, column 0 (harmless)
         }
     }
-
-    // ---- rows this tile looks at ----
-    const int r0 = tileRow[t], rE = tileRow[t + 1];
-    const int nEmit = rE - r0;                // rows that end inside this tile
-    const int ne = min(rE + 1, n_rows) - r0;  // row ends the walk may compare against
-    const bool inSmem = ne <= KMAX;
-    if (inSmem) {
-        for (int k = tid; k < ne; k += THREADS) sEnd[k] = (unsigned short)min(rowPtr[r0 + 1 + k] - base, 0xFFFF);
-        if (tid == 0) sEnd[ne] = 0xFFFF;
+    for (int i = tid; i < T / 32; i += THREADS) {
+        sFlag[i] = 0u;
+        sFirst[i] = INT_MAX;
     }
-    const bool headOpen = (r0 < n_rows) && (rowPtr[r0] < base);  // first row began in an earlier tile
-
-    // ---- products ----
-    A p[IPT];
+    const int r0 = tileRow[t], nEmit = tileRow[t + 1] - r0;  // rows that end inside this tile
+    const bool headOpen = cPtr[r0] < base;                   // the first of them began in an earlier tile
+    __syncthreads();
+    for (int k = tid; k < nEmit; k += THREADS) {
+        const int e = cPtr[r0 + 1 + k] - base - 1;  // in [0, cnt): rows are non-empty, so ends are distinct
+        atomicOr(&sFlag[e >> 5], 1u << (e & 31));
+        atomicMin(&sFirst[e >> 5], k);
+    }
 #pragma unroll
-    for (int j = 0; j < IPT; ++j) p[j] = v[j] * to_acc(__ldg(x + c[j]));
+    for (int j = 0; j < IPT; ++j) sp[pidx<A>(tid + j * THREADS)] = v[j] * to_acc(__ldg(x + c[j]));
     __syncthreads();
 
-    auto rowEnd = [&](int k) -> int {
-        if (inSmem) return sEnd[k];
-        return k < ne ? rowPtr[r0 + 1 + k] - base : INT_MAX;
-    };
-    int k = 0;  // row (relative to r0) the thread's first product belongs to
-    if (tid != 0) {
-        int lo = 0, hi = ne;
-        while (lo < hi) {
-            int mid = (lo + hi) >> 1;
-            if (rowEnd(mid) <= a)
-                lo = mid + 1;
-            else
-                hi = mid;
-        }
-        k = lo;
-    }
-    A acc = A(0), headAcc = A(0);
-    int headK = -1;
-    int e = rowEnd(k);
-    auto emit = [&]() {
-        if (headK < 0) {  // first row this thread finishes: it may have begun in an earlier thread
-            headK = k;
-            headAcc = acc;
-        } else if (inSmem) {
-            ysum[k] = acc;
-        } else {
-            store_row<V, HAS_TILE, MODE>(out, r0 + k, acc);
-        }
-        acc = A(0);
-        ++k;
-        e = rowEnd(k);
-    };
+    // ---- phase B: every thread owns IPT consecutive products ----
+    const int a = tid * IPT;
+    A p[IPT];
+    {
+        const A *src = sp + pidx<A>(a);  // IPT <= 16: the chunk never crosses a padding slot
+        if constexpr (sizeof(A) == 4) {
 #pragma unroll
-    for (int j = 0; j < IPT; ++j) {
-        const int i = a + j;
-        if (i < cnt) {
-            while (i >= e) emit();
-            acc += p[j];
+            for (int q = 0; q < IPT / 4; ++q) {
+                float4 f = *reinterpret_cast<const float4 *>(src + 4 * q);
+                p[4 * q] = f.x;
+                p[4 * q + 1] = f.y;
+                p[4 * q + 2] = f.z;
+                p[4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < IPT / 2; ++q) {
+                double2 d = *reinterpret_cast<const double2 *>(src + 2 * q);
+                p[2 * q] = d.x;
+                p[2 * q + 1] = d.y;
+            }
         }
     }
-    while (k < nEmit && e <= a + IPT) emit();
+    const unsigned word = sFlag[a >> 5];
+    const unsigned mask = (word >> (a & 31)) & ((1u << IPT) - 1u);
+    const bool hasEnd = mask != 0u;
+    // row (relative to r0) closed by this thread's first set bit
+    const int k0 = sFirst[a >> 5] + __popc(word & ((1u << (a & 31)) - 1u));
+    int k = k0;
+    A acc = A(0);
+#pragma unroll
+    for (int j = 0; j < IPT; ++j) {  // branch-free walk: a set bit closes a row
+        acc += p[j];
+        if ((mask >> j) & 1u) {
+            ysum[k] = acc;
+            ++k;
+            acc = A(0);
+        }
+    }
 
-    // ---- key-segmented inclusive scan of the (row, partial) tails over the tile ----
-    int key = k;
+    // ---- what a thread has left after its last closed row belongs to a row closed by a later thread:
+    //      segmented inclusive scan of these tails; a thread that closed a row starts a new segment ----
+    const unsigned hm = __ballot_sync(0xffffffffu, hasEnd);
+    const unsigned upto = hm & (0xffffffffu >> (31 - lane));  // lanes <= this one that closed a row
+    const int segStart = upto ? 31 - __clz(upto) : 0;
     A sv = acc;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        int k2 = __shfl_up_sync(0xffffffffu, key, d);
-        A v2 = __shfl_up_sync(0xffffffffu, sv, d);
-        if (lane >= d && k2 == key) sv += v2;
+        A o = __shfl_up_sync(0xffffffffu, sv, d);
+        if (lane - d >= segStart) sv += o;
     }
+    A pv = __shfl_up_sync(0xffffffffu, sv, 1);  // tails left by the lanes before this one
     if (lane == 31) {
-        warpKey[w] = key;
-        warpVal[w] = sv;
+        warpTail[w] = sv;
+        warpOpen[w] = hm == 0u;
     }
     __syncthreads();
-    int ck = -1;  // carry into this warp
-    A cv = A(0);
-    if (w > 0) {
-        ck = warpKey[w - 1];
-        for (int u = 0; u < w; ++u)
-            if (warpKey[u] == ck) cv += warpVal[u];
+    A cv = A(0);  // tails left by earlier warps for the row that is open at this warp's start
+    for (int u = w - 1; u >= 0; --u) {
+        cv += warpTail[u];
+        if (!warpOpen[u]) break;
     }
-    int pk = __shfl_up_sync(0xffffffffu, key, 1);
-    A pv = __shfl_up_sync(0xffffffffu, sv, 1);
-    if (lane == 0) {
-        pk = ck;
+    const bool openToWarpStart = (hm & ((1u << lane) - 1u)) == 0u;  // no lane before this one closed a row
+    if (lane == 0)
         pv = cv;
-    } else if (pk == ck) {
+    else if (openToWarpStart)
         pv += cv;
-    }
-    if (headK >= 0) {
-        A hv = headAcc + (pk == headK ? pv : A(0));
-        if (headK == 0 && headOpen)
-            head[t] = hv;  // the fix-up kernel finishes rows that span tiles
-        else if (inSmem)
-            ysum[headK] = hv;
-        else
-            store_row<V, HAS_TILE, MODE>(out, r0 + headK, hv);
-    }
-    if (tid == THREADS - 1) carry[t] = sv + (key == ck ? cv : A(0));
-    if (!inSmem) return;  // block-uniform
+    if (hasEnd) ysum[k0] += pv;  // the first row this thread closed began in earlier threads
+    if (tid == THREADS - 1) carry[t] = sv + (upto == 0u ? cv : A(0));
     __syncthreads();
+
     // ---- coalesced epilogue: one row per thread per pass ----
-    for (int q = tid + (headOpen ? 1 : 0); q < nEmit; q += THREADS) store_row<V, HAS_TILE, MODE>(out, r0 + q, ysum[q]);
+    if (headOpen && nEmit > 0 && tid == 0) head[t] = ysum[0];  // the fix-up kernel finishes rows that span tiles
+    for (int q = tid + (headOpen ? 1 : 0); q < nEmit; q += THREADS) {
+        const int r = out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q;
+        store_row<V, HAS_TILE, MODE>(out, r, ysum[q]);
+    }
 }
 
 // Rows that span tiles: sum the carries of the tiles the row passed through, in tile order, then the head.
+// The same launch writes the empty rows (their y is 0, or the tile-half contribution).
 template <typename V, int IPT, bool HAS_TILE, int MODE>
-__global__ void resid_fixup_kernel(const int *__restrict__ rowPtr, RowOut<V> out, const int *__restrict__ tileRow,
+__global__ void resid_fixup_kernel(const int *__restrict__ cPtr, RowOut<V> out, const int *__restrict__ tileRow,
                                    const typename AccOf<V>::T *__restrict__ carry,
-                                   const typename AccOf<V>::T *__restrict__ head, int n_rows, int num_tiles) {
+                                   const typename AccOf<V>::T *__restrict__ head, int m_rows, int num_tiles,
+                                   const int *__restrict__ emptyRow, int n_empty) {
     using A = typename AccOf<V>::T;
     constexpr int T = RESID_THREADS * IPT;
-    int t = blockIdx.x * blockDim.x + threadIdx.x + 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_empty) store_row<V, HAS_TILE, MODE>(out, emptyRow[i], A(0));
+    const int t = i + 1;
     if (t >= num_tiles) return;
-    int r0 = tileRow[t];
-    if (r0 >= n_rows || tileRow[t + 1] <= r0) return;  // no row ends in this tile
-    int start = rowPtr[r0];
+    const int r0 = tileRow[t];
+    if (r0 >= m_rows || tileRow[t + 1] <= r0) return;  // no row ends in this tile
+    const int start = cPtr[r0];
     if (start >= t * T) return;  // the first row begins inside the tile
     A s = A(0);
     for (int u = start / T; u < t; ++u) s += carry[u];
     s += head[t];
-    store_row<V, HAS_TILE, MODE>(out, r0, s);
+    store_row<V, HAS_TILE, MODE>(out, out.nzRow ? out.nzRow[r0] : r0, s);
 }
 
 template <typename V>
@@ -304,17 +312,18 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     out.row_map = row_map;
     out.ytile = (const A *)ytile;
     out.hotmask = hotmask;
+    out.nzRow = P.nz_row;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
-    int fgrid = (P.num_tiles - 1 + 127) / 128;
+    const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
+    const int fgrid = (fwork + 127) / 128;
 #define MX_LAUNCH(HT, MD)                                                                                          \
     do {                                                                                                           \
-        resid_kernel<V, IPT, HT, MD><<<grid, block, 0, s>>>(P.row_ptr, P.col_ind, (const V *)P.val, (const V *)x,  \
-                                                            out, P.tile_row, (A *)P.carry, (A *)P.head, P.n_rows,  \
-                                                            P.nnz);                                                \
+        resid_kernel<V, IPT, HT, MD><<<grid, block, 0, s>>>(P.c_ptr, P.col_ind, (const V *)P.val, (const V *)x,    \
+                                                            out, P.tile_row, (A *)P.carry, (A *)P.head, P.nnz);   \
         if (fgrid > 0)                                                                                             \
-            resid_fixup_kernel<V, IPT, HT, MD><<<fgrid, 128, 0, s>>>(P.row_ptr, out, P.tile_row,                   \
-                                                                     (const A *)P.carry, (const A *)P.head,       \
-                                                                     P.n_rows, P.num_tiles);                      \
+            resid_fixup_kernel<V, IPT, HT, MD><<<fgrid, 128, 0, s>>>(P.c_ptr, out, P.tile_row, (const A *)P.carry, \
+                                                                     (const A *)P.head, P.m_rows, P.num_tiles,    \
+                                                                     P.empty_row, P.n_empty);                     \
     } while (0)
     if (mode == OUT_CARRIER)
         MX_LAUNCH(false, OUT_CARRIER);
@@ -336,23 +345,57 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &P, cudaStream_t s) {
     P.tile_nnz = RESID_THREADS * (dtype == MX_FP64 ? ResidCfg<double>::IPT : ResidCfg<__half>::IPT);
     P.num_tiles = P.nnz > 0 ? (int)(((long long)P.nnz + P.tile_nnz - 1) / P.tile_nnz) : 1;
     cudaError_t e;
+    // rows without entries leave the kernel's row space: cPtr = row pointers of the non-empty rows
+    int *flag = nullptr, *pos = nullptr;
+    const size_t nr = (size_t)P.n_rows + 1;
+    if ((e = cudaMalloc(&flag, nr * sizeof(int))) != cudaSuccess) return e;
+    if ((e = cudaMalloc(&pos, nr * sizeof(int))) != cudaSuccess) return e;
+    nonempty_flag_kernel<<<(int)((nr + 255) / 256), 256, 0, s>>>(P.row_ptr, P.n_rows, flag);
+    {
+        TempBuf tmp;
+        if ((e = exclusive_sum(tmp, flag, pos, (int)nr, s)) != cudaSuccess) return e;
+        if ((e = cudaMemcpyAsync(&P.m_rows, pos + P.n_rows, sizeof(int), cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+            return e;
+        if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    }
+    P.n_empty = P.n_rows - P.m_rows;
+    if (P.n_empty == 0) {
+        P.c_ptr = P.row_ptr;
+        P.nz_row = nullptr;
+        P.empty_row = nullptr;
+    } else {
+        if ((e = cudaMalloc(&P.c_ptr_own, ((size_t)P.m_rows + 1) * sizeof(int))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&P.nz_row, ((size_t)P.m_rows + 1) * sizeof(int))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&P.empty_row, (size_t)P.n_empty * sizeof(int))) != cudaSuccess) return e;
+        compress_rows_kernel<<<(P.n_rows + 255) / 256, 256, 0, s>>>(P.row_ptr, pos, P.n_rows, P.c_ptr_own, P.nz_row,
+                                                                    P.empty_row);
+        P.c_ptr = P.c_ptr_own;
+    }
     if ((e = cudaMalloc(&P.tile_row, sizeof(int) * (size_t)(P.num_tiles + 1))) != cudaSuccess) return e;
     if ((e = cudaMalloc(&P.carry, acc_bytes(dtype) * (size_t)P.num_tiles)) != cudaSuccess) return e;
     if ((e = cudaMalloc(&P.head, acc_bytes(dtype) * (size_t)P.num_tiles)) != cudaSuccess) return e;
-    tile_row_kernel<<<(P.num_tiles + 1 + 255) / 256, 256, 0, s>>>(P.row_ptr, P.n_rows, P.nnz, P.tile_nnz, P.num_tiles,
+    tile_row_kernel<<<(P.num_tiles + 1 + 255) / 256, 256, 0, s>>>(P.c_ptr, P.m_rows, P.nnz, P.tile_nnz, P.num_tiles,
                                                                   P.tile_row);
-    return cudaGetLastError();
+    e = cudaGetLastError();
+    cudaError_t e2 = cudaStreamSynchronize(s);
+    cudaFree(flag);
+    cudaFree(pos);
+    return e != cudaSuccess ? e : e2;
 }
 
 void resid_plan_free(ResidPlan &P) {
     cudaFree(P.tile_row);
     cudaFree(P.carry);
     cudaFree(P.head);
-    P.tile_row = nullptr;
+    cudaFree(P.c_ptr_own);
+    cudaFree(P.nz_row);
+    cudaFree(P.empty_row);
+    P.tile_row = P.c_ptr_own = P.nz_row = P.empty_row = nullptr;
+    P.c_ptr = nullptr;
     P.carry = P.head = nullptr;
 }
 
-int resid_launches(const ResidPlan &P) { return P.num_tiles > 1 ? 2 : 1; }
+int resid_launches(const ResidPlan &P) { return (P.num_tiles > 1 || P.n_empty > 0) ? 2 : 1; }
 
 cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, const void *ytile,
                        const uint32_t *hotmask, bool accumulate, int *, cudaStream_t s) {

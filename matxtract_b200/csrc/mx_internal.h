@@ -34,7 +34,12 @@ struct ResidPlan {
     const int *col_ind = nullptr;  // [nnz]
     const void *val = nullptr;     // [nnz]
     int tile_nnz = 0, num_tiles = 0;
-    int *tile_row = nullptr;   // [num_tiles+1] rows whose end lies at or before the tile's first non-zero
+    int m_rows = 0, n_empty = 0;     // non-empty / empty rows
+    const int *c_ptr = nullptr;      // [m_rows+1] row pointers of the non-empty rows (= row_ptr when none is empty)
+    int *c_ptr_own = nullptr;        // storage of c_ptr when it is not row_ptr
+    int *nz_row = nullptr;           // [m_rows] k-th non-empty row -> row index (null: identity)
+    int *empty_row = nullptr;        // [n_empty]
+    int *tile_row = nullptr;   // [num_tiles+1] non-empty rows whose end lies at or before the tile's first non-zero
     void *carry = nullptr;     // [num_tiles] accumulate-type partial of the tile's unfinished last row
     void *head = nullptr;      // [num_tiles] accumulate-type partial of a first row that began in an earlier tile
 };
