@@ -127,7 +127,6 @@ __device__ __forceinline__ double ldg_stream_val(const double *p) {
     asm volatile("ld.global.nc.L1::evict_first.f64 %0, [%1];" : "=d"(r) : "l"(p));
     return r;
 }
-
 // 16 bytes of padding after every 16 products: the striped stores of phase A and the 128-bit blocked
 // loads of phase B are then both free of bank conflicts.
 template <typename A>
@@ -146,7 +145,7 @@ __global__ void __launch_bounds__(RESID_THREADS, 4)
     constexpr int NW = THREADS / 32;
     constexpr int PADW = 16 / (int)sizeof(A);
     __shared__ __align__(16) A sp[T + (T / 16) * PADW];  // products, padded
-    __shared__ A ysum[T];                                // sums of the rows that end in this tile
+    A *const ysum = sp;  // sums of the rows that end in this tile: reuses the buffer once the products are in registers
     __shared__ unsigned sFlag[T / 32];                   // bit i set: a row ends after the tile's i-th non-zero
     __shared__ int sFirst[T / 32];                       // lowest row (relative) that ends inside the 32-nnz word
     __shared__ A warpTail[NW];
@@ -157,7 +156,7 @@ __global__ void __launch_bounds__(RESID_THREADS, 4)
     const int cnt = min(T, nnz - base);
 
     // ---- phase A: lane <-> consecutive non-zeros: coalesced streams, and gathers that coalesce on runs of
-    //      consecutive columns ----
+    //      consecutive columns (a 4-wide lane mapping and a shared-memory x window were measured: both slower) ----
     int c[IPT];
     A v[IPT];
     const int *cb = colInd + base + tid;
@@ -220,6 +219,7 @@ __global__ void __launch_bounds__(RESID_THREADS, 4)
     const bool hasEnd = mask != 0u;
     // row (relative to r0) closed by this thread's first set bit
     const int k0 = sFirst[a >> 5] + __popc(word & ((1u << (a & 31)) - 1u));
+    __syncthreads();  // every product is in registers: the buffer now holds row sums
     int k = k0;
     A acc = A(0);
 #pragma unroll
