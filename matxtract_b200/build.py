@@ -17,8 +17,6 @@ CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 OBJDIR = LIBDIR / "obj"
 LIB = LIBDIR / "libmatxtract_b200.so"
-HOST_LIB = LIBDIR / "libMatXtract_host.so"
-PERFTEST = LIBDIR / "matxtract_perftest"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -73,17 +71,18 @@ def build_all(verbose: bool = False, force: bool = False, ptxas_info: bool = Fal
     if host.exists():
         for tag, define in (("fp64", ["-Dfp64"]), ("fp16", [])):
             shim = LIBDIR / f"libMatXtract_{tag}.so"
-            srcs = [host / "MatXtract_api.cpp"]
+            srcs = [host / "MatXtract_api.cpp", host / "mm_reader.cpp"]
             if any(_newer(s, shim, headers) for s in srcs) or force or _newer(LIB, shim):
                 _run(["/usr/bin/g++", "-std=c++17", "-O2", "-fPIC", "-shared", *define, f"-I{ROOT / 'include'}",
                       "-I/usr/local/cuda/include", *srcs, f"-L{LIBDIR}", "-lmatxtract_b200",
                       "-Wl,-rpath,$ORIGIN", "-o", shim], verbose)
             exe = LIBDIR / f"matxtract_perftest_{tag}"
-            srcs = [host / "matxtract_perftest.cpp", host / "mm_reader.cpp"]
+            srcs = [host / "matxtract_perftest.cpp"]
             if all(s.exists() for s in srcs) and (any(_newer(s, exe, headers) for s in srcs) or force or _newer(shim, exe)):
                 _run(["/usr/bin/g++", "-std=c++17", "-O2", *define, f"-I{ROOT / 'include'}",
                       "-I/usr/local/cuda/include", *srcs, f"-L{LIBDIR}", f"-lMatXtract_{tag}", "-lmatxtract_b200",
-                      "-Wl,-rpath,$ORIGIN", "-o", exe], verbose)
+                      "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64",
+                      "-o", exe], verbose)
     return LIB
 
 

@@ -1,0 +1,105 @@
+"""Row-partitioned SpMV over several GPUs of one box: one process per GPU, x replicated, y all-gathered.
+
+The reference is single-GPU; the partition follows the usual 1-D scheme: contiguous row slabs with boundaries at
+``lower_bound(row_ptr, g * nnz / G)`` so that every rank streams the same number of non-zeros.  Each rank extracts and
+multiplies its own slab (``rows_g x all columns``) with its own (tau_c, tau_r) partition; parity across ranks is on y.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def nnz_balanced_bounds(row_ptr: np.ndarray, world: int) -> list[int]:
+    """Row boundaries b[0]=0 <= ... <= b[world]=n with ~nnz/world non-zeros per slab."""
+    row_ptr = np.asarray(row_ptr)
+    n, nnz = len(row_ptr) - 1, int(row_ptr[-1])
+    b = [int(np.searchsorted(row_ptr, (g * nnz) // world, side="left")) for g in range(world)] + [n]
+    b[0] = 0
+    for g in range(1, world + 1):  # monotone even with empty leading rows
+        b[g] = max(b[g], b[g - 1])
+    return b
+
+
+def equal_row_bounds(n: int, world: int) -> list[int]:
+    return [(g * n) // world for g in range(world)] + [n]
+
+
+def slab(row_ptr, col_ind, val, r0: int, r1: int):
+    """CSR of rows [r0, r1) with row pointers rebased to 0."""
+    lo, hi = int(row_ptr[r0]), int(row_ptr[r1])
+    return (np.asarray(row_ptr[r0:r1 + 1], np.int32) - lo).astype(np.int32), col_ind[lo:hi], val[lo:hi]
+
+
+def all_gather_rows(y_local, bounds, group=None):
+    """Assembles the full y from every rank's slice (unequal sizes allowed).  Works on NCCL and gloo tensors."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    sizes = [bounds[g + 1] - bounds[g] for g in range(world)]
+    if len(set(sizes)) == 1:
+        out = torch.empty(sum(sizes), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(out, y_local.contiguous(), group=group)
+        return out
+    # unequal slabs: pad every slice to the longest one, gather once, cut the padding out (same code on NCCL and gloo)
+    longest = max(sizes)
+    padded = torch.zeros(longest, dtype=y_local.dtype, device=y_local.device)
+    padded[: y_local.numel()] = y_local
+    out = torch.empty(world * longest, dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(out, padded, group=group)
+    return torch.cat([out[g * longest: g * longest + sizes[g]] for g in range(world)])
+
+
+class DistributedSpMV:
+    """This rank's slab on its GPU plus the collective that assembles y.
+
+    ``local_spmv`` (x_full -> y_slab tensor) can be injected to exercise the host-side logic without a GPU; by default
+    the slab runs through a :class:`matxtract_b200.MatXtract` handle on ``device``.
+    """
+
+    def __init__(self, dtype, n_cols, row_ptr, col_ind, val, rank, world, tau=(0.0, 0.0), device=None, balance="nnz",
+                 local_spmv=None, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        n = len(row_ptr) - 1
+        self.bounds = nnz_balanced_bounds(row_ptr, world) if balance == "nnz" else equal_row_bounds(n, world)
+        r0, r1 = self.bounds[rank], self.bounds[rank + 1]
+        self.rows = r1 - r0
+        rp, ci, v = slab(row_ptr, col_ind, val, r0, r1)
+        self.local_nnz = int(rp[-1])
+        self._local = local_spmv
+        self.handle = None
+        if local_spmv is None:
+            import torch
+
+            from . import MatXtract
+
+            self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+            self.handle = MatXtract(dtype, device=self.device.index)
+            self.handle.upload_csr(self.rows, n_cols, rp, ci, v)
+            self.stats = self.handle.partition(*tau)
+            self.stream = torch.cuda.ExternalStream(self.handle.stream, device=self.device)
+            tdt = torch.float64 if dtype == 0 else torch.float16
+            self._y = torch.zeros(max(self.rows, 1), dtype=tdt, device=self.device)[: self.rows]
+        else:
+            self._slab = (rp, ci, v)
+
+    def spmv(self, x_full):
+        """y = A x for the whole matrix (every rank returns the full y)."""
+        import torch
+
+        if self._local is not None:
+            y_local = self._local(self._slab, x_full)
+            return all_gather_rows(y_local, self.bounds, self.group)
+        self.handle.spmv(x_full, self._y)
+        with torch.cuda.stream(self.stream):
+            return all_gather_rows(self._y, self.bounds, self.group)
+
+    def close(self):
+        if self.handle is not None:
+            import torch
+
+            self.stream.synchronize()
+            self._y = None
+            torch.cuda.synchronize()
+            self.handle.close()
+            self.handle = None
