@@ -25,7 +25,8 @@ enum {
     MX_ERR_OVERFLOW = 5, /* a count does not fit the reference's int32 index type */
     MX_ERR_TIMEOUT = 6,  /* a bounded device-side wait ran out */
     MX_ERR_NOMEM = 7,
-    MX_ERR_NO_DEVICE = 8 /* no CUDA device: there is no CPU fallback */
+    MX_ERR_NO_DEVICE = 8, /* no CUDA device: there is no CPU fallback */
+    MX_ERR_TOO_LARGE = 9  /* the matrix exceeds the fixed scratch of mx_csr_spmv_static */
 };
 
 /* Value type of a handle.  The reference fixes it at compile time (-Dfp64, include/common.h:53-70):
@@ -132,6 +133,23 @@ int mx_du_tcspmv(int dtype, const int *chunkPtr, const int *fragPtr, const void 
  * Y_val[i] is the result for input row order_rid[i]; this implementation returns the identity order. */
 int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColIdx, const void *x, void *y,
                  int *order_rid, int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv);
+
+/* ---- allocation-free CSR SpMV (no counterpart in the reference: every reference wrapper allocates) ---------- */
+/* y = A x for a CSR matrix that is already on the device, for callers that must not allocate device memory at call
+ * time: code running inside a fixed memory arena, a real-time loop that may not block on the driver's allocator, a
+ * process whose memory budget was fixed at start-up.  The call performs no cudaMalloc / cudaFree and uses no library
+ * routine that allocates; all pointers are DEVICE pointers supplied by the caller (y is overwritten).  The scratch the
+ * kernels need lives in a fixed array inside the library image (MX_STATIC_SCRATCH_BYTES per GPU, held until the
+ * process exits), which bounds the problem: at most MX_STATIC_MAX_ROWS rows and MX_STATIC_MAX_NNZ non-zeros, else
+ * MX_ERR_TOO_LARGE.  All calls share that array: do not let two calls overlap on the GPU (they would race on it).
+ * The call synchronises `stream` once (it reads one count back).  The first call on a device looks up the array's
+ * device address; make that first call before starting any stream capture.  `stream` is a cudaStream_t (NULL = the
+ * default stream). */
+#define MX_STATIC_MAX_ROWS (1 << 20)
+#define MX_STATIC_MAX_NNZ (1 << 26)
+#define MX_STATIC_SCRATCH_BYTES (24u << 20)
+int mx_csr_spmv_static(int dtype, int n_rows, int n_cols, int nnz, const int *row_ptr_dev, const int *col_ind_dev,
+                       const void *val_dev, const void *x_dev, void *y_dev, void *stream);
 
 /* ---- synthetic inputs (host code) ----------------------------------------------------------------- */
 enum { MX_SYNTH_UNIFORM = 0, MX_SYNTH_POWERLAW = 1, MX_SYNTH_BLOCK = 2, MX_SYNTH_HOTCOL = 3 };

@@ -11,7 +11,7 @@ DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
 
 STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
-          6: "MX_ERR_TIMEOUT", 7: "MX_ERR_NOMEM", 8: "MX_ERR_NO_DEVICE"}
+          6: "MX_ERR_TIMEOUT", 7: "MX_ERR_NOMEM", 8: "MX_ERR_NO_DEVICE", 9: "MX_ERR_TOO_LARGE"}
 
 
 class MxError(RuntimeError):
@@ -67,6 +67,7 @@ SYMBOLS = {
     "mx_cdspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d), C.POINTER(_d)]),
     "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
     "mx_se_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d)]),
+    "mx_csr_spmv_static": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx_synth_row_lengths": (_i, [C.POINTER(SynthParams), C.c_int64, C.c_int64, _vp]),
     "mx_synth_fill": (_i, [C.POINTER(SynthParams), _i, C.c_int64, C.c_int64, _vp, _vp, _vp]),
     "mx_synth_vector": (_i, [C.c_uint64, _i, C.c_int64, C.c_int64, _vp]),
@@ -249,3 +250,10 @@ def se_tcspmv(dtype, val, row_ptr, col_ind, x_d, warm=0, iters=0):
     _raise(lib().mx_se_tcspmv(dtype, _ptr(val), _ptr(row_ptr), _ptr(col_ind), _ptr(x_d), _ptr(y), _ptr(order), rows,
                               len(x_d), len(col_ind), warm, iters, C.byref(ms)))
     return y, order, ms.value
+
+
+def csr_spmv_static(dtype, n_rows, n_cols, nnz, row_ptr_dev, col_ind_dev, val_dev, x_dev, y_dev, stream=0):
+    """y = A x through the allocation-free entry point: all arrays are device pointers (ints) or CUDA tensors."""
+    st = lib().mx_csr_spmv_static(dtype, n_rows, n_cols, nnz, _ptr(row_ptr_dev), _ptr(col_ind_dev), _ptr(val_dev),
+                                  _ptr(x_dev), _ptr(y_dev), C.c_void_p(stream))
+    _raise(st)

@@ -421,3 +421,140 @@ cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *out, 
 }
 
 }  // namespace mx
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free CSR SpMV.
+//
+// Some callers of this library run where device memory cannot be requested: a solver that was handed a fixed
+// arena and must not touch the allocator, a real-time loop that may not block on the driver's allocation lock, a
+// process whose memory budget was fixed at start-up.  For them this entry point computes y = A x for a CSR matrix
+// that already lives on the device with NO cudaMalloc / cudaFree (and no library call that allocates): everything the
+// kernels need beyond the caller's inputs and output — the compressed row table, the per-tile row offsets and the
+// carry / head slots of rows that span tiles — lives in the fixed array below.
+//
+// The array is part of the library image: every GPU that loads the library holds MX_STATIC_SCRATCH_BYTES of it until
+// the process exits.  All calls share it and it keeps what the last call left there, so (a) the slots that a call
+// reads before writing are cleared at the start of every call, and (b) two calls that overlap on the GPU (different
+// streams, or different host threads) race on it — issue them one after the other.
+// In host code `g_static_scratch` is only a stand-in for the device symbol, not a device address: its address is
+// looked up once per device with cudaGetSymbolAddress (with that device current) and that pointer is what the kernels
+// get.  The first call on a device performs this look-up, so it should happen before any stream capture begins.
+// ---------------------------------------------------------------------------------------------------------------
+namespace mx {
+namespace {
+
+constexpr size_t ST_ROWS = MX_STATIC_MAX_ROWS;
+constexpr size_t ST_TILES = (size_t)MX_STATIC_MAX_NNZ / (RESID_THREADS * ResidCfg<double>::IPT) + 1;  // FP64 tiles are the smaller
+constexpr size_t ST_CUB_TEMP = 1u << 20;
+// layout (byte offsets, each region 256-byte aligned)
+constexpr size_t st_align(size_t b) { return (b + 255) & ~(size_t)255; }
+constexpr size_t ST_OFF_FLAG = 0;
+constexpr size_t ST_OFF_POS = ST_OFF_FLAG + st_align((ST_ROWS + 1) * 4);
+constexpr size_t ST_OFF_CPTR = ST_OFF_POS + st_align((ST_ROWS + 1) * 4);
+constexpr size_t ST_OFF_NZROW = ST_OFF_CPTR + st_align((ST_ROWS + 1) * 4);
+constexpr size_t ST_OFF_EMPTY = ST_OFF_NZROW + st_align((ST_ROWS + 1) * 4);
+constexpr size_t ST_OFF_TILEROW = ST_OFF_EMPTY + st_align((ST_ROWS + 1) * 4);
+constexpr size_t ST_OFF_CARRY = ST_OFF_TILEROW + st_align((ST_TILES + 1) * 4);
+constexpr size_t ST_OFF_HEAD = ST_OFF_CARRY + st_align(ST_TILES * 8);
+constexpr size_t ST_OFF_TEMP = ST_OFF_HEAD + st_align(ST_TILES * 8);
+constexpr size_t ST_TOTAL = ST_OFF_TEMP + ST_CUB_TEMP;
+static_assert(ST_TOTAL <= MX_STATIC_SCRATCH_BYTES, "scratch layout exceeds the size stated in mx_capi.h");
+
+static __device__ __align__(256) unsigned char g_static_scratch[MX_STATIC_SCRATCH_BYTES];
+
+constexpr int ST_MAX_DEVICES = 64;
+unsigned char *g_static_ptr[ST_MAX_DEVICES] = {};  // device address of g_static_scratch, per device
+
+// once per device, with that device current
+cudaError_t static_scratch_address(unsigned char **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= ST_MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = g_static_ptr[dev];
+    return cudaSuccess;
+}
+
+}  // namespace
+}  // namespace mx
+
+extern "C" int mx_csr_spmv_static(int dtype, int n_rows, int n_cols, int nnz, const int *row_ptr_dev,
+                                  const int *col_ind_dev, const void *val_dev, const void *x_dev, void *y_dev,
+                                  void *stream) {
+    using namespace mx;
+    if ((dtype != MX_FP64 && dtype != MX_FP16) || n_rows < 0 || n_cols < 0 || nnz < 0 || !row_ptr_dev || !x_dev ||
+        !y_dev || (nnz > 0 && (!col_ind_dev || !val_dev)))
+        return MX_ERR_INVALID;
+    if ((size_t)n_rows > ST_ROWS || (long long)nnz > (long long)MX_STATIC_MAX_NNZ) {
+        fprintf(stderr,
+                "mx_csr_spmv_static: %d rows / %d non-zeros exceed the fixed scratch (at most %d rows, %d non-zeros); "
+                "use a handle (mx_create / mx_upload_csr / mx_spmv) for larger matrices\n",
+                n_rows, nnz, (int)MX_STATIC_MAX_ROWS, (int)MX_STATIC_MAX_NNZ);
+        return MX_ERR_TOO_LARGE;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = nullptr;
+    if (static_scratch_address(&base) != cudaSuccess) {
+        cudaGetLastError();
+        return MX_ERR_CUDA;
+    }
+    int *flag = reinterpret_cast<int *>(base + ST_OFF_FLAG), *pos = reinterpret_cast<int *>(base + ST_OFF_POS);
+    ResidPlan P;
+    P.n_rows = n_rows;
+    P.n_cols = n_cols;
+    P.nnz = nnz;
+    P.row_ptr = row_ptr_dev;
+    P.col_ind = col_ind_dev;
+    P.val = val_dev;
+    P.tile_nnz = RESID_THREADS * (dtype == MX_FP64 ? ResidCfg<double>::IPT : ResidCfg<__half>::IPT);
+    P.num_tiles = nnz > 0 ? (int)(((long long)nnz + P.tile_nnz - 1) / P.tile_nnz) : 1;
+    P.tile_row = reinterpret_cast<int *>(base + ST_OFF_TILEROW);
+    P.carry = base + ST_OFF_CARRY;
+    P.head = base + ST_OFF_HEAD;
+#define STCK(call)                            \
+    do {                                      \
+        if ((call) != cudaSuccess) {          \
+            cudaGetLastError();               \
+            return MX_ERR_CUDA;               \
+        }                                     \
+    } while (0)
+    // the array keeps the previous call's contents: clear the slots that are read before they are written
+    STCK(cudaMemsetAsync(P.carry, 0, acc_bytes(dtype) * (size_t)P.num_tiles, s));
+    STCK(cudaMemsetAsync(P.head, 0, acc_bytes(dtype) * (size_t)P.num_tiles, s));
+    // rows without entries leave the kernel's row space (same steps as resid_plan_build, on the fixed array)
+    const size_t nr = (size_t)n_rows + 1;
+    nonempty_flag_kernel<<<(int)((nr + 255) / 256), 256, 0, s>>>(row_ptr_dev, n_rows, flag);
+    size_t temp_bytes = 0;
+    STCK(cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, flag, pos, (int)nr, s));
+    if (temp_bytes > ST_CUB_TEMP) return MX_ERR_TOO_LARGE;
+    STCK(cub::DeviceScan::ExclusiveSum(base + ST_OFF_TEMP, temp_bytes, flag, pos, (int)nr, s));
+    int m_rows = 0;
+    STCK(cudaMemcpyAsync(&m_rows, pos + n_rows, sizeof(int), cudaMemcpyDeviceToHost, s));
+    STCK(cudaStreamSynchronize(s));
+    P.m_rows = m_rows;
+    P.n_empty = n_rows - m_rows;
+    if (P.n_empty == 0) {
+        P.c_ptr = row_ptr_dev;
+    } else {
+        int *cptr = reinterpret_cast<int *>(base + ST_OFF_CPTR);
+        P.nz_row = reinterpret_cast<int *>(base + ST_OFF_NZROW);
+        P.empty_row = reinterpret_cast<int *>(base + ST_OFF_EMPTY);
+        compress_rows_kernel<<<(n_rows + 255) / 256, 256, 0, s>>>(row_ptr_dev, pos, n_rows, cptr, P.nz_row, P.empty_row);
+        P.c_ptr = cptr;
+    }
+    tile_row_kernel<<<(P.num_tiles + 1 + 255) / 256, 256, 0, s>>>(P.c_ptr, P.m_rows, P.nnz, P.tile_nnz, P.num_tiles,
+                                                                  P.tile_row);
+    STCK(cudaGetLastError());
+    cudaError_t e = dtype == MX_FP64
+                        ? resid_spmv_t<double>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s)
+                        : resid_spmv_t<__half>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s);
+    STCK(e);
+#undef STCK
+    return MX_OK;
+}

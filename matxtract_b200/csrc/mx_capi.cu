@@ -119,6 +119,7 @@ const char *mx_status_string(int status) {
         case MX_ERR_TIMEOUT: return "bounded device wait ran out";
         case MX_ERR_NOMEM: return "out of memory";
         case MX_ERR_NO_DEVICE: return "no CUDA device (this library has no CPU fallback)";
+        case MX_ERR_TOO_LARGE: return "matrix exceeds the fixed scratch of the allocation-free entry point";
     }
     return "unknown status";
 }
