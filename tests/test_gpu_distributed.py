@@ -1,0 +1,60 @@
+"""Row-partitioned SpMV on 2 GPUs (one process per GPU, NCCL all-gather of y).  Skipped on a single-GPU box."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+import matxtract_b200 as mx
+from matxtract_b200 import synth, distributed as D
+import oracle
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+for name, n, tau in (("c2", 60000, (0.46, 0.33)), ("c3", 8 * 4000, (0.5, 0.5)), ("c5", 50000, (0.0, 0.0))):
+    m = synth.generate(name, n=n)
+    dtype = m["dtype"]
+    d = D.DistributedSpMV(dtype, n, m["row_ptr"], m["col_ind"], m["val"], rank, world, tau=tau)
+    x = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).cuda()
+    x = x.view(torch.float16) if dtype == mx.FP16 else x
+    d.stream.wait_stream(torch.cuda.current_stream())
+    y = d.spmv(x)
+    d.stream.synchronize()
+    y = y.cpu().numpy()
+    y_ref = oracle.spmv_serial(dtype, m["row_ptr"], m["col_ind"], m["val"], m["x"])
+    err = oracle.y_error(dtype, y, y_ref, m["row_ptr"], m["col_ind"], m["val"], m["x"])
+    assert err <= (1e-12 if dtype == mx.FP64 else 2e-3), (name, err)
+    assert sum(d.bounds[g + 1] - d.bounds[g] for g in range(world)) == n
+    del y, x
+    d.close()
+    print(f"rank {rank} {name} ok err={err:.2e} rows={d.rows} nnz={d.local_nnz}", flush=True)
+dist.destroy_process_group()
+'''
+
+
+def test_two_rank_row_partition_matches_the_oracle(tmp_path):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), str(ROOT)],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count(" ok ") == 6
