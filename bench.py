@@ -234,6 +234,9 @@ def run_ours(args):
     st = h.partition(*tau)
     if args.dd != "auto":
         h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR}[args.dd])
+    if args.colspace != "auto":
+        h.set_column_space({"permuted": mx.COLSPACE_PERMUTED, "original": mx.COLSPACE_ORIGINAL}[args.colspace])
+    colspace = h.column_space
     stream = torch.cuda.ExternalStream(h.stream, device=torch.device("cuda", local))
 
     x_host = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).pin_memory()
@@ -360,6 +363,8 @@ def run_ours(args):
         "algorithmic_bytes_per_step": b_alg_total,
         "partition": {k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
         "dd_executor": {1: "tile (tensor cores)", 2: "csr (CUDA cores)"}.get(h.dd_executor, "none"),
+        "column_space": {"in_use": {1: "permuted", 2: "original"}.get(colspace[0], "n/a"),
+                         "tuned_ms_permuted": colspace[1], "tuned_ms_original": colspace[2]},
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms,
         "ms_tile_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
@@ -386,6 +391,8 @@ def main():
     ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
     ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr"], help="executor of the core-dense block")
+    ap.add_argument("--colspace", default="auto", choices=["auto", "permuted", "original"],
+                    help="column numbering used for execution")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

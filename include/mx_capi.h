@@ -114,6 +114,15 @@ enum { MX_DD_AUTO = 0, MX_DD_TILE = 1, MX_DD_CSR = 2 };
 #define MX_DD_AUTO_FILL 0.25
 int mx_set_dd_executor(mx_handle_t h, int mode);
 int mx_dd_executor(mx_handle_t h); /* the one in use: MX_DD_TILE or MX_DD_CSR */
+/* Column numbering used for EXECUTION (the partition arrays, and what mx_download_partition returns, always use the
+ * reference's numbering).  MX_COLSPACE_PERMUTED: hot columns first in density-rank order, as the reference executes
+ * (x is permuted on the device at every product; pays when few hot columns carry much of the matrix).
+ * MX_COLSPACE_ORIGINAL: the same entries with their original column ids (x is read directly; keeps the matrix's own
+ * locality).  MX_COLSPACE_AUTO (default): mx_partition times both on the device and keeps the faster. */
+enum { MX_COLSPACE_AUTO = 0, MX_COLSPACE_PERMUTED = 1, MX_COLSPACE_ORIGINAL = 2 };
+int mx_set_column_space(mx_handle_t h, int mode);
+/* the one in use; optionally the two timings (ms per product) of the last automatic choice */
+int mx_column_space(mx_handle_t h, float *ms_permuted, float *ms_original);
 /* Number of kernel launches one mx_spmv issues for the current matrix / partition. */
 int mx_spmv_launches(mx_handle_t h);
 /* Device error word of the last kernels (0 = none). */

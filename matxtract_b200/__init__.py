@@ -5,6 +5,9 @@ The package is a thin Python view of ``libmatxtract_b200.so`` (hand-written CUDA
 inspected), but creating a handle without a CUDA device raises.
 """
 from .capi import (  # noqa: F401
+    COLSPACE_AUTO,
+    COLSPACE_ORIGINAL,
+    COLSPACE_PERMUTED,
     DD_AUTO,
     DD_CSR,
     DD_TILE,

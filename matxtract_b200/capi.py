@@ -8,6 +8,7 @@ import numpy as np
 
 FP64, FP16 = 0, 1
 DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
+COLSPACE_AUTO, COLSPACE_PERMUTED, COLSPACE_ORIGINAL = 0, 1, 2
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
 
 STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
@@ -63,6 +64,8 @@ SYMBOLS = {
     "mx_spmv_launches": (_i, [_vp]),
     "mx_set_dd_executor": (_i, [_vp, _i]),
     "mx_dd_executor": (_i, [_vp]),
+    "mx_set_column_space": (_i, [_vp, _i]),
+    "mx_column_space": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_device_error": (_i, [_vp, _ip]),
     "mx_cdspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d), C.POINTER(_d)]),
     "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
@@ -188,6 +191,17 @@ class MatXtract:
     def set_dd_executor(self, mode: int):
         """0 = auto (by fill ratio), 1 = tensor-core tile kernel, 2 = CSR kernel on the core-dense block."""
         self._ck(lib().mx_set_dd_executor(self._h, mode))
+
+    def set_column_space(self, mode: int):
+        """0 = auto (timed at partition time), 1 = the partition's permuted numbering, 2 = original column ids."""
+        self._ck(lib().mx_set_column_space(self._h, mode))
+
+    @property
+    def column_space(self):
+        """(mode in use, ms per product permuted, ms per product original) of the last automatic choice."""
+        a, b = C.c_float(), C.c_float()
+        m = lib().mx_column_space(self._h, C.byref(a), C.byref(b))
+        return m, a.value, b.value
 
     @property
     def dd_executor(self) -> int:

@@ -294,6 +294,12 @@ __global__ void resid_fixup_kernel(const int *__restrict__ cPtr, RowOut<V> out, 
     store_row<V, HAS_TILE, MODE>(out, out.nzRow ? out.nzRow[r0] : r0, s);
 }
 
+__global__ void map_indices_kernel(const int *__restrict__ in, const int *__restrict__ map, int *__restrict__ out,
+                                   long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __ldg(map + __ldg(in + i));
+}
+
 template <typename V>
 __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ perm, V *__restrict__ out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -408,6 +414,12 @@ cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, 
                                   cudaStream_t s) {
     if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
     return resid_spmv_t<__half>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
+}
+
+cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    map_indices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, map, out, n);
+    return cudaGetLastError();
 }
 
 cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *out, int n, cudaStream_t s) {

@@ -26,6 +26,12 @@ struct mx_handle_s {
     ResidPlan ddcsr;         // the core-dense block as CSR, for the low-fill executor
     int dd_mode = MX_DD_AUTO;
     bool dd_use_tile = true;
+    // execution column space: the partition numbers columns by density rank (x must be permuted every product);
+    // the same entries with their ORIGINAL column ids read x directly and keep the matrix's own locality
+    int colspace_mode = MX_COLSPACE_AUTO;
+    bool use_orig_cols = false;
+    int *colInd_CD_orig = nullptr, *colInd_dd_orig = nullptr, *AToX_orig = nullptr;
+    float tune_ms_perm = 0, tune_ms_orig = 0;
     void *ytile = nullptr;   // [n_rows] accumulate-type carrier of the tile half
     void *x_perm = nullptr;  // [n_cols] x in partition order
     // staging for the host-pointer entry point
@@ -57,6 +63,11 @@ void drop_plan(mx_handle_t h) {
     part_arrays_free(h->part);
     cudaFree(h->ytile);
     cudaFree(h->x_perm);
+    cudaFree(h->colInd_CD_orig);
+    cudaFree(h->colInd_dd_orig);
+    cudaFree(h->AToX_orig);
+    h->colInd_CD_orig = h->colInd_dd_orig = h->AToX_orig = nullptr;
+    h->use_orig_cols = false;
     h->ytile = h->x_perm = nullptr;
     h->planned = false;
     h->stats = mx_partition_stats{};
@@ -193,6 +204,69 @@ int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row
     return MX_OK;
 }
 
+// points the execution plans at the column numbering in use
+static void select_colspace(mx_handle_t h, bool orig) {
+    h->use_orig_cols = orig;
+    h->resid.col_ind = orig ? h->colInd_CD_orig : h->part.colInd_CD;
+    h->ddcsr.col_ind = orig ? h->colInd_dd_orig : h->part.colInd_dd;
+    h->tile.A.AToX = orig ? h->AToX_orig : h->part.tiles.AToX;
+}
+
+// the core-dense block: tensor-core tile kernel, or (low fill) the CSR kernel on the same entries
+static cudaError_t dd_enqueue(mx_handle_t h, const void *x) {
+    if (h->dd_use_tile)
+        return tile_spmv(h->dtype, h->tile, x, h->ytile, h->part.rId, true, false, h->dev_err, h->stream);
+    return resid_spmv_to_carrier(h->dtype, h->ddcsr, x, h->ytile, h->part.rId, h->stream);
+}
+
+static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid,
+                        bool permute = true) {
+    if (h->stats.active) {
+        const void *x = x_dev;
+        if (!h->use_orig_cols) {
+            if (permute) HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
+            x = h->x_perm;
+        }
+        if (do_tile) HCK(dd_enqueue(h, x));
+        if (do_resid)
+            HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->dev_err, h->stream));
+    } else if (do_resid) {
+        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->dev_err, h->stream));
+    }
+    return MX_OK;
+}
+
+// times the whole product in both column spaces on scratch vectors and keeps the faster
+static int tune_colspace(mx_handle_t h) {
+    h->tune_ms_perm = h->tune_ms_orig = 0;
+    if (h->colspace_mode != MX_COLSPACE_AUTO) {
+        select_colspace(h, h->colspace_mode == MX_COLSPACE_ORIGINAL);
+        return MX_OK;
+    }
+    cudaEvent_t e0, e1;
+    HCK(cudaEventCreate(&e0));
+    HCK(cudaEventCreate(&e1));
+    HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
+    float ms[2] = {0, 0};
+    for (int space = 0; space < 2; ++space) {
+        select_colspace(h, space == 1);
+        for (int i = 0; i < 3 + 10; ++i) {
+            if (i == 3) HCK(cudaEventRecord(e0, h->stream));
+            int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, true);
+            if (st != MX_OK) return st;
+        }
+        HCK(cudaEventRecord(e1, h->stream));
+        HCK(cudaEventSynchronize(e1));
+        HCK(cudaEventElapsedTime(&ms[space], e0, e1));
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    h->tune_ms_perm = ms[0] / 10;
+    h->tune_ms_orig = ms[1] / 10;
+    select_colspace(h, ms[1] < ms[0]);
+    return MX_OK;
+}
+
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats) {
     if (!h) return MX_ERR_INVALID;
     if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_partition: no matrix uploaded");
@@ -262,6 +336,20 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         HCK(cudaMalloc(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows));
         HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
         HCK(cudaMalloc(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols));
+        // the same entries numbered by their original columns
+        const size_t nAToX = (size_t)h->stats.totalFrags * h->stats.fragK;
+        HCK(cudaMalloc(&h->colInd_CD_orig, sizeof(int) * (size_t)(h->stats.nnzCD > 0 ? h->stats.nnzCD : 1)));
+        HCK(cudaMalloc(&h->colInd_dd_orig, sizeof(int) * (size_t)(h->stats.nnzRowD > 0 ? h->stats.nnzRowD : 1)));
+        HCK(cudaMalloc(&h->AToX_orig, sizeof(int) * (nAToX > 0 ? nAToX : 1)));
+        HCK(map_indices(h->part.colInd_CD, h->part.xperm, h->colInd_CD_orig, h->stats.nnzCD, h->stream));
+        HCK(map_indices(h->part.colInd_dd, h->part.xperm, h->colInd_dd_orig, h->stats.nnzRowD, h->stream));
+        HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
+        h->planned = true;  // the tuner runs real products
+        int tst = tune_colspace(h);
+        if (tst != MX_OK) {
+            drop_plan(h);
+            return tst;
+        }
     }
     HCK(cudaEventRecord(e1, h->stream));
     HCK(cudaEventSynchronize(e1));
@@ -311,26 +399,6 @@ int mx_download_partition(mx_handle_t h, const mx_partition_arrays *o) {
     return MX_OK;
 }
 
-// the core-dense block: tensor-core tile kernel, or (low fill) the CSR kernel on the same entries
-static cudaError_t dd_enqueue(mx_handle_t h) {
-    if (h->dd_use_tile)
-        return tile_spmv(h->dtype, h->tile, h->x_perm, h->ytile, h->part.rId, true, false, h->dev_err, h->stream);
-    return resid_spmv_to_carrier(h->dtype, h->ddcsr, h->x_perm, h->ytile, h->part.rId, h->stream);
-}
-
-static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid) {
-    if (h->stats.active) {
-        HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
-        if (do_tile) HCK(dd_enqueue(h));
-        if (do_resid)
-            HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
-                           h->stream));
-    } else if (do_resid) {
-        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->dev_err, h->stream));
-    }
-    return MX_OK;
-}
-
 int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev) {
     if (!h || !x_dev || !y_dev) return MX_ERR_INVALID;
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv: call mx_partition first");
@@ -354,7 +422,8 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
 int mx_spmv_launches(mx_handle_t h) {
     if (!h || !h->planned) return 0;
     int n = resid_launches(h->resid);
-    if (h->stats.active) n += 1 + (h->dd_use_tile ? tile_launches(h->tile) : resid_launches(h->ddcsr));
+    if (h->stats.active)
+        n += (h->use_orig_cols ? 0 : 1) + (h->dd_use_tile ? tile_launches(h->tile) : resid_launches(h->ddcsr));
     return n;
 }
 
@@ -364,6 +433,24 @@ int mx_set_dd_executor(mx_handle_t h, int mode) {
     if (h->planned && h->stats.active)
         h->dd_use_tile = mode == MX_DD_TILE || (mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
     return MX_OK;
+}
+
+int mx_set_column_space(mx_handle_t h, int mode) {
+    if (!h || mode < MX_COLSPACE_AUTO || mode > MX_COLSPACE_ORIGINAL) return MX_ERR_INVALID;
+    h->colspace_mode = mode;
+    if (h->planned && h->stats.active) {
+        HCK(cudaSetDevice(h->device));
+        HCK(cudaStreamSynchronize(h->stream));
+        return tune_colspace(h);
+    }
+    return MX_OK;
+}
+
+int mx_column_space(mx_handle_t h, float *ms_permuted, float *ms_original) {
+    if (!h || !h->planned || !h->stats.active) return MX_COLSPACE_AUTO;
+    if (ms_permuted) *ms_permuted = h->tune_ms_perm;
+    if (ms_original) *ms_original = h->tune_ms_orig;
+    return h->use_orig_cols ? MX_COLSPACE_ORIGINAL : MX_COLSPACE_PERMUTED;
 }
 
 int mx_dd_executor(mx_handle_t h) {
@@ -398,12 +485,7 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
                 st = spmv_enqueue(h, x_dev, y_dev, true, true);
             } else if (h->stats.active) {
                 // one half alone, on an x that is already permuted (the reference times its halves the same way)
-                st = MX_OK;
-                if (i == 0) HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
-                if (do_tile) HCK(dd_enqueue(h));
-                if (do_resid)
-                    HCK(resid_spmv(h->dtype, h->resid, h->x_perm, y_dev, h->ytile, h->part.hotmask, false, h->dev_err,
-                                   h->stream));
+                st = spmv_enqueue(h, x_dev, y_dev, do_tile, do_resid, /*permute=*/i == 0);
             } else {
                 st = spmv_enqueue(h, x_dev, y_dev, false, true);
             }

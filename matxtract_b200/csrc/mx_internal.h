@@ -114,6 +114,8 @@ cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_d
 void part_arrays_free(PartArrays &P);
 void tile_arrays_free(TileArrays &T);
 
+// out[i] = map[in[i]]
+cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s);
 // x_perm[i] = x[perm[i]]
 cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *x_perm, int n, cudaStream_t s);
 

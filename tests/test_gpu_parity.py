@@ -84,12 +84,16 @@ def test_partition_bit_exact_and_split_spmv(dtype, tau, case):
     h.upload_csr(n, n, rp, ci, val)
     h.partition(*tau)
     assert_partition_equal(dtype, h, o)
-    for mode in (mx.DD_TILE, mx.DD_CSR, mx.DD_AUTO):  # both executors of the core-dense block
-        h.set_dd_executor(mode)
-        assert mode == mx.DD_AUTO or h.dd_executor == mode
-        y = h.spmv_host(x)
-        check_y(dtype, y, rp, ci, val, x)
-        np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
+    for space in (mx.COLSPACE_PERMUTED, mx.COLSPACE_ORIGINAL, mx.COLSPACE_AUTO):  # both execution numberings
+        h.set_column_space(space)
+        assert space == mx.COLSPACE_AUTO or h.column_space[0] == space
+        for mode in (mx.DD_TILE, mx.DD_CSR, mx.DD_AUTO):  # both executors of the core-dense block
+            h.set_dd_executor(mode)
+            assert mode == mx.DD_AUTO or h.dd_executor == mode
+            y = h.spmv_host(x)
+            check_y(dtype, y, rp, ci, val, x)
+            np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
+    assert_partition_equal(dtype, h, o)  # the execution numbering never changes the partition arrays
     assert h.device_error() == 0
     h.close()
 
@@ -204,11 +208,13 @@ def test_benchmark_shapes_at_reduced_size(name, n, tau):
     h.partition(*tau)
     if tau != (0.0, 0.0):
         assert_partition_equal(dtype, h, oracle.partition(dtype, n, n, rp, ci, val, *tau))
-    for mode in (mx.DD_TILE, mx.DD_CSR):
-        h.set_dd_executor(mode)
-        y = h.spmv_host(x)
-        check_y(dtype, y, rp, ci, val, x)
-        np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
+    for space in ((mx.COLSPACE_PERMUTED, mx.COLSPACE_ORIGINAL) if tau != (0.0, 0.0) else (mx.COLSPACE_AUTO,)):
+        h.set_column_space(space)
+        for mode in (mx.DD_TILE, mx.DD_CSR):
+            h.set_dd_executor(mode)
+            y = h.spmv_host(x)
+            check_y(dtype, y, rp, ci, val, x)
+            np.testing.assert_array_equal(_bits(y), _bits(h.spmv_host(x)))
     assert h.device_error() == 0
     h.close()
 
