@@ -83,6 +83,10 @@ def build_all(verbose: bool = False, force: bool = False, ptxas_info: bool = Fal
                       "-I/usr/local/cuda/include", *srcs, f"-L{LIBDIR}", f"-lMatXtract_{tag}", "-lmatxtract_b200",
                       "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64",
                       "-o", exe], verbose)
+    probe = CSRC / "probe" / "gather_ceiling.cu"
+    exe = LIBDIR / "gather_ceiling"
+    if probe.exists() and (force or _newer(probe, exe)):
+        _run([NVCC, *ARCH, "-O3", "-ccbin", "/usr/bin/g++", probe, "-o", exe], verbose)
     return LIB
 
 

@@ -1,6 +1,7 @@
 // C ABI of libmatxtract_b200.so: handle management, matrix upload, extraction, SpMV, timing loops, and the
 // stateless mirrors of the reference's host API (include/MatXtract.h).  See include/mx_capi.h.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -103,7 +104,7 @@ struct DevBufs {  // frees on scope exit
     int n = 0;
     template <typename T>
     cudaError_t up(T **d, const void *src, size_t bytes) {
-        cudaError_t e = cudaMalloc((void **)d, bytes > 0 ? bytes : 1);
+        cudaError_t e = cudaMalloc((void **)d, bytes + 64);  // slack: the tile kernel's bulk copies round up to 16 bytes
         if (e != cudaSuccess) return e;
         p[n++] = *d;
         if (src && bytes > 0) e = cudaMemcpy(*d, src, bytes, cudaMemcpyHostToDevice);

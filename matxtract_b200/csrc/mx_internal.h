@@ -74,6 +74,10 @@ struct TilePlan {
     int *panelFirstSeg = nullptr;   // [chunkNum+1]
     void *partial = nullptr;        // [numMultiSegs][8] accumulate-type partial sums
     unsigned *panelCount = nullptr; // [chunkNum] arrival counters of split panels (self-resetting)
+    // CTAs own runs of consecutive segments sized by the bytes they stage in shared memory
+    int numCtas = 0, stageBytes = 0;  // grid size; largest stage (dynamic shared memory per CTA)
+    void *ctaDesc = nullptr;          // [numCtas] descriptors
+    void *segDesc = nullptr;          // [numSegs] packed {panel, first fragment, end fragment, slot}
 };
 
 // Everything the extraction produces, on the device (owned).

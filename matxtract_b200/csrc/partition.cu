@@ -296,10 +296,10 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
         *status = MX_ERR_OVERFLOW;
         totalFrags = 0;
     }
-    PCK(dalloc(&T.AToX, (size_t)totalFrags * K));
-    PCK(dalloc((B **)&T.fragBit, (size_t)totalFrags));
-    PCK(dalloc(&T.fragPtr, (size_t)totalFrags + 1));
-    PCK(dalloc((V **)&T.tcVal, (size_t)nnzRowD));
+    PCK(dalloc(&T.AToX, (size_t)totalFrags * K + 8));  // +slack: bulk copies round up to 16 bytes
+    PCK(dalloc((B **)&T.fragBit, (size_t)totalFrags + 8));
+    PCK(dalloc(&T.fragPtr, (size_t)totalFrags + 1 + 8));
+    PCK(dalloc((V **)&T.tcVal, (size_t)nnzRowD + 16));
     PCK(sc.alloc(&pc, (size_t)totalFrags + 1));
     PCK(sc.alloc(&entFrag, (size_t)nnzRowD));
     PCK(sc.alloc(&entBit, (size_t)nnzRowD));

@@ -11,13 +11,22 @@
 //       B column 0  = x-segments of f and f+1,      B column 1  = x-segments of f+2 and f+3,
 //     so C[r][0] + C[8+r][1] is the panel row's sum over the four fragments (the cross terms land in
 //     columns that are never read).  Lane l owns bitmap bits 2l and 2l+1 of every fragment.
-//   * Bitmaps, value offsets and x indices of 8 fragments are fetched with one coalesced load each and
-//     handed round with warp shuffles; the gathered x values likewise (one gather per lane).
-//   * Sums stay in the accumulator registers over the whole fragment run; one store per row, no atomics
-//     on y.  The reference gives every panel one warp; a power-law panel can hold 10^4 fragments, so
-//     here a panel is cut into segments of at most SEG fragments, one warp each.  Segments of a split
-//     panel park their 8 partial sums; the last one to arrive (a counter, no spinning) adds them in
-//     segment order, so the result does not depend on arrival order.
+//   * A CTA owns a run of consecutive work segments; their bitmaps, value offsets, x indices and packed values are
+//     four contiguous ranges, which one thread copies into shared memory with 1-D bulk copies (cp.async.bulk on an
+//     mbarrier, bounded wait).  Warps then run their segments out of shared memory: broadcast shared loads for the
+//     bitmap and the offset, conflict-free shared loads for the values, and each lane gathers the x value of its own
+//     fragment column (4 distinct addresses per instruction) — no shuffles, no dependent global loads but the gathers.
+//   * Sums stay in the accumulator registers over the whole fragment run (two independent chains for FP64); one store
+//     per row, no atomics on y.  The reference gives every panel one warp; a power-law panel can hold 10^4
+//     fragments, so here a panel is cut into segments of at most SEG fragments, one warp each.  Segments of a split
+//     panel park their 8 partial sums; the last one to arrive (a counter, no spinning) adds them in segment order.
+//   * Measured and dropped: direct global loads with shuffle hand-round (37 warp-instructions per fragment, 193 us on
+//     the 100M-nnz block matrix vs 115 us now), gathering x into shared memory behind a CTA-wide barrier (164 us), a
+//     persistent 4-stage ring with one producer warp and 4 consumer warps per CTA (275 us: throughput follows the
+//     number of resident consumer warps, not the copies in flight).  Stage size sweep 8-64 KB: best at 16 KB x 4 warps.
+#include <cstdlib>
+#include <type_traits>
+
 #include "device_prims.cuh"
 #include "mx_internal.h"
 
@@ -25,7 +34,6 @@ namespace mx {
 namespace {
 
 constexpr int SEG = 64;            // fragments per work segment
-constexpr int TILE_WARPS = 4;      // warps per CTA
 
 __global__ void seg_count_kernel(const int *__restrict__ chunkPtr, int chunkNum, int *__restrict__ segCount,
                                  int *__restrict__ multiCount) {
@@ -62,16 +70,16 @@ __device__ __forceinline__ double get(const double *o) { return *o; }
 __device__ __forceinline__ float get(const float *o) { return *o; }
 __device__ __forceinline__ float get(const __half *o) { return __half2float(*o); }
 
-// Hands the 8 row sums of one segment over: directly to `out` when the panel has a single segment,
-// through `partial` + arrival counter otherwise.  rowLane: this lane holds the sum of panel row g.
+// Hands the 8 row sums of one segment over: directly to `out` when the panel has a single segment, through `partial`
+// and an arrival counter otherwise (the last segment of the panel to arrive adds the parked sums in segment order, so
+// the result does not depend on arrival order; nobody spins).  rowLane: this lane holds the sum of panel row g.  The
+// slot comes with the packed segment descriptor and the output row was looked up before the fragment loop; slots of a
+// split panel are consecutive from its first segment.
 template <typename A, typename OutT, bool ACCUM>
-__device__ __forceinline__ void finish_segment(A sum, bool rowLane, int g, int lane, int p, int s, int dRows,
-                                               const int *__restrict__ segSlot,
-                                               const int *__restrict__ panelFirstSeg, A *__restrict__ partial,
-                                               unsigned *__restrict__ panelCount, OutT *__restrict__ out,
-                                               const int *__restrict__ row_map) {
-    const int row = p * 8 + g;
-    const int slot = segSlot[s];
+__device__ __forceinline__ void finish_staged(A sum, bool rowLane, int g, int lane, int p, int s, int slot, int myRow,
+                                              int outRow, int dRows, const int *__restrict__ panelFirstSeg,
+                                              A *__restrict__ partial, unsigned *__restrict__ panelCount,
+                                              OutT *__restrict__ out) {
     if (slot >= 0) {
         if (rowLane) __stcg(partial + (size_t)slot * 8 + g, sum);
         __threadfence();
@@ -83,108 +91,157 @@ __device__ __forceinline__ void finish_segment(A sum, bool rowLane, int g, int l
         if (old != (unsigned)(nseg - 1)) return;  // not the last segment of the panel to finish
         __threadfence();
         if (lane == 0) panelCount[p] = 0;  // ready for the next launch
-        const int slot0 = segSlot[first];
+        const int slot0 = slot - (s - first);
         sum = A(0);
         if (rowLane)
             for (int j = 0; j < nseg; ++j) sum += __ldcg(partial + (size_t)(slot0 + j) * 8 + g);
     }
-    if (rowLane && row < dRows) {
-        const int o = row_map ? row_map[row] : row;
-        if (ACCUM) sum += (A)get(out + o);
-        put(out + o, sum);
+    if (rowLane && myRow < dRows) {
+        if (ACCUM) sum += (A)get(out + outRow);
+        put(out + outRow, sum);
     }
 }
 
-template <typename OutT, bool ACCUM>
-__global__ void __launch_bounds__(TILE_WARPS * 32)
-    tile_kernel_fp64(const double *__restrict__ x_d, const int *__restrict__ fragPtr,
-                     const uint32_t *__restrict__ fragBit, const double *__restrict__ tcVal,
-                     const int *__restrict__ AToX, const int *__restrict__ segPanel, const int *__restrict__ segBegin,
-                     const int *__restrict__ segEnd, const int *__restrict__ segSlot,
-                     const int *__restrict__ panelFirstSeg, double *__restrict__ partial,
-                     unsigned *__restrict__ panelCount, OutT *__restrict__ out, const int *__restrict__ row_map,
-                     int dRows, int numSegs) {
-    const int lane = threadIdx.x & 31;
-    const int s = blockIdx.x * TILE_WARPS + (threadIdx.x >> 5);
-    if (s >= numSegs) return;
-    const int p = segPanel[s], f0 = segBegin[s], f1 = segEnd[s];
-    const uint32_t below = (1u << lane) - 1u;
-    double c0 = 0.0, c1 = 0.0;
-    for (int f = f0; f < f1; f += 8) {
-        const int nb = min(8, f1 - f);
-        const uint32_t bm_l = lane < nb ? __ldg(fragBit + f + lane) : 0u;
-        const int ptr_l = lane < nb ? __ldg(fragPtr + f + lane) : 0;
-        const int xi = (lane >> 2) < nb ? __ldg(AToX + (size_t)f * 4 + lane) : -1;
-        const double xv = xi >= 0 ? __ldg(x_d + xi) : 0.0;
-        double a[8], b[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t bm = __shfl_sync(0xffffffffu, bm_l, j);
-            const int ptr = __shfl_sync(0xffffffffu, ptr_l, j);
-            b[j] = __shfl_sync(0xffffffffu, xv, 4 * j + (lane & 3));
-            a[j] = ((bm >> lane) & 1u) ? __ldg(tcVal + ptr + __popc(bm & below)) : 0.0;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
+// ------------------------------------------------------------------------------------------------------------------
+// TMA staging.  A CTA owns a run of consecutive work segments; because segments are consecutive, the bitmaps,
+// value offsets, x indices and packed values they touch are four contiguous ranges.  One elected thread copies the
+// four ranges into shared memory with 1-D bulk copies (cp.async.bulk, completion counted on an mbarrier, no
+// multicast); every warp then runs its segments out of shared memory, so the fragment loop has no dependent global
+// load left except the x gathers.  Several CTAs per SM overlap one CTA's copies with another's arithmetic.
+// ------------------------------------------------------------------------------------------------------------------
+struct CtaDesc {  // computed at plan time
+    int seg0, seg1;  // work segments [seg0, seg1)
+    int f0, f1;      // fragments [f0, f1) they cover
+    int v0, v1;      // packed values [v0, v1)
+    int pad0, pad1;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// waits for phase 0 of the barrier; gives up after a bounded number of polls (returns false)
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar) {
+    const uint32_t a = smem_u32(bar);
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(0u)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+constexpr int STAGE_WARPS_MAX = 8;
+int g_stage_warps = 4;           // warps per CTA (4 or 8)
+int g_stage_bytes = 16 * 1024;   // target bytes per CTA; a CTA may exceed it by one segment (sweep: 8-64 KB)
+
+// byte layout of a CTA's shared-memory stage; every range starts 16-byte aligned in global AND shared memory
+template <typename B, typename V, int K>
+struct StageLayout {
+    int fa, va;                  // fragment / value index the copies start at (rounded down to 16 bytes)
+    uint32_t nBit, nPtr, nX, nV;  // copy sizes in bytes (multiples of 16)
+    uint32_t oBit, oPtr, oX, oV;  // offsets in the stage
+    __host__ __device__ StageLayout(int f0, int f1, int v0, int v1) {
+        constexpr int FA = 16 / (int)sizeof(B) > 4 ? 16 / (int)sizeof(B) : 4;  // covers bitmaps and the int offsets
+        constexpr int VA = 16 / (int)sizeof(V);
+        fa = f0 & ~(FA - 1);
+        va = v0 & ~(VA - 1);
+        auto up16 = [](size_t b) { return (uint32_t)((b + 15) & ~(size_t)15); };
+        nBit = up16((size_t)(f1 - fa) * sizeof(B));
+        nPtr = up16((size_t)(f1 + 1 - fa) * 4);
+        nX = up16((size_t)(f1 - f0) * K * 4);
+        nV = up16((size_t)(v1 - va) * sizeof(V));
+        oBit = 16;  // the first 16 bytes hold the mbarrier
+        oPtr = oBit + nBit;
+        oX = oPtr + nPtr;
+        oV = oX + nX;
+    }
+    __host__ __device__ uint32_t total() const { return oV + nV; }
+};
+
+// one work segment, run out of a landed stage
+template <typename B, typename V, int K, typename OutT, bool ACCUM>
+__device__ __forceinline__ void run_segment(const int4 sd, int s, int lane, const B *sBit, const int *sPtr,
+                                            const int *sX, const V *sVal, const V *__restrict__ x_d,
+                                            const int *__restrict__ panelFirstSeg,
+                                            typename std::conditional<sizeof(V) == 8, double, float>::type *partial,
+                                            unsigned *panelCount, OutT *out, const int *row_map, int dRows) {
+    const int p = sd.x, f0 = sd.y, f1 = sd.z;
+    // where the row this lane may store goes: asked for before the fragment loop so that it is there afterwards
+    const int myRow = p * 8 + (lane >> 2);
+    const int outRow = (row_map && myRow < dRows) ? __ldg(row_map + myRow) : myRow;
+    if constexpr (sizeof(V) == 8) {
+        const uint32_t below = (1u << lane) - 1u;
+        const int kx = lane & 3;
+        double c0 = 0.0, c1 = 0.0, e0 = 0.0, e1 = 0.0;  // two independent accumulator chains
+        int f = f0;
+#pragma unroll 4
+        for (; f + 1 < f1; f += 2) {
+            const uint32_t bmA = (uint32_t)sBit[f], bmB = (uint32_t)sBit[f + 1];
+            const double aA = ((bmA >> lane) & 1u) ? sVal[sPtr[f] + __popc(bmA & below)] : 0.0;
+            const double aB = ((bmB >> lane) & 1u) ? sVal[sPtr[f + 1] + __popc(bmB & below)] : 0.0;
+            // every lane gathers the x value of its own fragment column: 4 distinct addresses per instruction
+            const double bA = __ldg(x_d + sX[(size_t)f * 4 + kx]), bB = __ldg(x_d + sX[(size_t)(f + 1) * 4 + kx]);
             asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
                          : "+d"(c0), "+d"(c1)
-                         : "d"(a[j]), "d"(b[j]));
-    }
-    // lane 4g holds C[g][0], the sum of panel row g
-    finish_segment<double, OutT, ACCUM>(c0, (lane & 3) == 0, lane >> 2, lane, p, s, dRows, segSlot, panelFirstSeg,
-                                        partial, panelCount, out, row_map);
-}
-
-template <typename OutT, bool ACCUM>
-__global__ void __launch_bounds__(TILE_WARPS * 32)
-    tile_kernel_fp16(const __half *__restrict__ x_d, const int *__restrict__ fragPtr,
-                     const uint64_t *__restrict__ fragBit, const __half *__restrict__ tcVal,
-                     const int *__restrict__ AToX, const int *__restrict__ segPanel, const int *__restrict__ segBegin,
-                     const int *__restrict__ segEnd, const int *__restrict__ segSlot,
-                     const int *__restrict__ panelFirstSeg, float *__restrict__ partial,
-                     unsigned *__restrict__ panelCount, OutT *__restrict__ out, const int *__restrict__ row_map,
-                     int dRows, int numSegs) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-    const int s = blockIdx.x * TILE_WARPS + (threadIdx.x >> 5);
-    if (s >= numSegs) return;
-    const int p = segPanel[s], f0 = segBegin[s], f1 = segEnd[s];
-    const int lo = 2 * lane;
-    const uint64_t below = (1ull << lo) - 1ull;
-    // source lanes of the packed x pairs this lane needs as B (column g of B; only g = 0, 1 are non-zero)
-    const int src0 = (g == 0) ? 2 * tq : 2 * (8 + tq);
-    const int src1 = src0 + 8;
-    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
-    for (int f = f0; f < f1; f += 8) {
-        const int nb = min(8, f1 - f);
-        const uint64_t bm_l = lane < nb ? __ldg(reinterpret_cast<const unsigned long long *>(fragBit) + f + lane) : 0ull;
-        const int ptr_l = lane < nb ? __ldg(fragPtr + f + lane) : 0;
-        const int xi0 = (lane >> 3) < nb ? __ldg(AToX + (size_t)f * 8 + lane) : -1;
-        const int xi1 = 4 + (lane >> 3) < nb ? __ldg(AToX + (size_t)f * 8 + 32 + lane) : -1;
-        const unsigned xb0 = xi0 >= 0 ? (unsigned)__half_as_ushort(__ldg(x_d + xi0)) : 0u;
-        const unsigned xb1 = xi1 >= 0 ? (unsigned)__half_as_ushort(__ldg(x_d + xi1)) : 0u;
-        // even lane 2q now holds x pair q = (column 2q', 2q'+1) of fragment q/4
-        const unsigned pair0 = xb0 | (__shfl_down_sync(0xffffffffu, xb0, 1) << 16);
-        const unsigned pair1 = xb1 | (__shfl_down_sync(0xffffffffu, xb1, 1) << 16);
-#pragma unroll
-        for (int m = 0; m < 2; ++m) {
-            if (m == 1 && nb <= 4) break;  // warp-uniform
-            const unsigned pair = m == 0 ? pair0 : pair1;
-            unsigned b0 = __shfl_sync(0xffffffffu, pair, src0);
-            unsigned b1 = __shfl_sync(0xffffffffu, pair, src1);
-            if (g > 1) {
-                b0 = 0u;
-                b1 = 0u;
-            }
+                         : "d"(aA), "d"(bA));
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                         : "+d"(e0), "+d"(e1)
+                         : "d"(aB), "d"(bB));
+        }
+        if (f < f1) {
+            const uint32_t bmA = (uint32_t)sBit[f];
+            const double aA = ((bmA >> lane) & 1u) ? sVal[sPtr[f] + __popc(bmA & below)] : 0.0;
+            const double bA = __ldg(x_d + sX[(size_t)f * 4 + kx]);
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                         : "+d"(c0), "+d"(c1)
+                         : "d"(aA), "d"(bA));
+        }
+        // lane 4g holds C[g][0], the sum of panel row g
+        finish_staged<double, OutT, ACCUM>(c0 + e0, (lane & 3) == 0, lane >> 2, lane, p, s, sd.w, myRow, outRow, dRows,
+                                           panelFirstSeg, (double *)partial, panelCount, out);
+    } else {
+        const int g = lane >> 2, tq = lane & 3;
+        const int lo = 2 * lane;
+        const uint64_t below = (1ull << lo) - 1ull;
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+        for (int f = f0; f < f1; f += 4) {
             unsigned a[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint64_t bm = __shfl_sync(0xffffffffu, bm_l, 4 * m + j);
-                const int ptr = __shfl_sync(0xffffffffu, ptr_l, 4 * m + j);
-                const int off = ptr + __popcll(bm & below);
-                const unsigned bit0 = (unsigned)(bm >> lo) & 1u, bit1 = (unsigned)(bm >> (lo + 1)) & 1u;
-                const unsigned h0 = bit0 ? (unsigned)__half_as_ushort(__ldg(tcVal + off)) : 0u;
-                const unsigned h1 = bit1 ? (unsigned)__half_as_ushort(__ldg(tcVal + off + bit0)) : 0u;
-                a[j] = h0 | (h1 << 16);
+                a[j] = 0u;
+                if (f + j < f1) {  // warp-uniform
+                    const uint64_t bm = (uint64_t)sBit[f + j];
+                    const int off = sPtr[f + j] + __popcll(bm & below);
+                    const unsigned bit0 = (unsigned)(bm >> lo) & 1u, bit1 = (unsigned)(bm >> (lo + 1)) & 1u;
+                    const unsigned h0 = bit0 ? (unsigned)__half_as_ushort(sVal[off]) : 0u;
+                    const unsigned h1 = bit1 ? (unsigned)__half_as_ushort(sVal[off + bit0]) : 0u;
+                    a[j] = h0 | (h1 << 16);
+                }
+            }
+            // B column g: g = 0 -> x-segments of fragments f, f+1; g = 1 -> of f+2, f+3; other columns zero
+            unsigned b0 = 0u, b1 = 0u;
+            if (g < 2) {
+                const int fb = f + 2 * g;
+                if (fb < f1) {
+                    const int2 ix = *reinterpret_cast<const int2 *>(sX + (size_t)fb * 8 + 2 * tq);
+                    b0 = (unsigned)__half_as_ushort(__ldg(x_d + ix.x)) |
+                         ((unsigned)__half_as_ushort(__ldg(x_d + ix.y)) << 16);
+                }
+                if (fb + 1 < f1) {
+                    const int2 ix = *reinterpret_cast<const int2 *>(sX + (size_t)(fb + 1) * 8 + 2 * tq);
+                    b1 = (unsigned)__half_as_ushort(__ldg(x_d + ix.x)) |
+                         ((unsigned)__half_as_ushort(__ldg(x_d + ix.y)) << 16);
+                }
             }
             // A registers: {rows g, k low} = frag 0, {rows g+8, k low} = frag 2, {rows g, k high} = frag 1,
             // {rows g+8, k high} = frag 3
@@ -194,10 +251,116 @@ __global__ void __launch_bounds__(TILE_WARPS * 32)
                 : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
                 : "r"(a[0]), "r"(a[2]), "r"(a[1]), "r"(a[3]), "r"(b0), "r"(b1));
         }
+        // lane 4g: c0 = C[g][0] (fragments f, f+1), c3 = C[g+8][1] (fragments f+2, f+3)
+        finish_staged<float, OutT, ACCUM>(c0 + c3, tq == 0, g, lane, p, s, sd.w, myRow, outRow, dRows, panelFirstSeg,
+                                          (float *)partial, panelCount, out);
     }
-    // lane 4g: c0 = C[g][0] (fragments f, f+1), c3 = C[g+8][1] (fragments f+2, f+3)
-    finish_segment<float, OutT, ACCUM>(c0 + c3, tq == 0, g, lane, p, s, dRows, segSlot, panelFirstSeg, partial,
-                                       panelCount, out, row_map);
+}
+
+template <typename B, typename V, int K, typename OutT, bool ACCUM, int STAGE_WARPS>
+__global__ void __launch_bounds__(STAGE_WARPS * 32)
+    tile_kernel_staged(const V *__restrict__ x_d, const int *__restrict__ fragPtr, const B *__restrict__ fragBit,
+                       const V *__restrict__ tcVal, const int *__restrict__ AToX, const CtaDesc *__restrict__ desc,
+                       const int4 *__restrict__ segDesc, const int *__restrict__ panelFirstSeg,
+                       typename std::conditional<sizeof(V) == 8, double, float>::type *__restrict__ partial,
+                       unsigned *__restrict__ panelCount, OutT *__restrict__ out, const int *__restrict__ row_map,
+                       int dRows, int *__restrict__ devErr) {
+    extern __shared__ __align__(16) unsigned char stage[];
+    uint64_t *bar = reinterpret_cast<uint64_t *>(stage);
+    const CtaDesc d = desc[blockIdx.x];
+    const StageLayout<B, V, K> L(d.f0, d.f1, d.v0, d.v1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t bytes = L.nBit + L.nPtr + L.nX + L.nV;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                     : "memory");
+        if (L.nX) bulk_g2s(stage + L.oX, AToX + (size_t)d.f0 * K, L.nX, bar);  // first: the x gathers wait on it
+        if (L.nBit) bulk_g2s(stage + L.oBit, fragBit + L.fa, L.nBit, bar);
+        if (L.nPtr) bulk_g2s(stage + L.oPtr, fragPtr + L.fa, L.nPtr, bar);
+        if (L.nV) bulk_g2s(stage + L.oV, tcVal + L.va, L.nV, bar);
+    }
+    if (!mbar_wait_bounded(bar)) {  // never expected; leaves a mark instead of spinning for ever
+        if (lane == 0 && devErr) atomicOr(devErr, DEVERR_TILE_RANGE);
+        return;
+    }
+    const B *sBit = reinterpret_cast<const B *>(stage + L.oBit) - L.fa;      // index with the global fragment id
+    const int *sPtr = reinterpret_cast<const int *>(stage + L.oPtr) - L.fa;  // "
+    const V *sVal = reinterpret_cast<const V *>(stage + L.oV) - L.va;        // index with the global value offset
+    const int *sX = reinterpret_cast<const int *>(stage + L.oX) - (size_t)d.f0 * K;  // index with fragment id * K + k
+
+    int s = d.seg0 + warp;
+    int4 sd = s < d.seg1 ? __ldg(segDesc + s) : make_int4(0, 0, 0, -1);
+    while (s < d.seg1) {
+        const int sn = s + STAGE_WARPS;
+        const int4 sdn = sn < d.seg1 ? __ldg(segDesc + sn) : make_int4(0, 0, 0, -1);  // next descriptor, early
+        run_segment<B, V, K, OutT, ACCUM>(sd, s, lane, sBit, sPtr, sX, sVal, x_d, panelFirstSeg, partial, panelCount,
+                                          out, row_map, dRows);
+        s = sn;
+        sd = sdn;
+    }
+}
+
+__global__ void seg_pack_kernel(const int *__restrict__ segPanel, const int *__restrict__ segBegin,
+                                const int *__restrict__ segEnd, const int *__restrict__ segSlot, int numSegs,
+                                int4 *__restrict__ segDesc) {
+    int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < numSegs) segDesc[s] = make_int4(segPanel[s], segBegin[s], segEnd[s], segSlot[s]);
+}
+
+// bytes a segment brings into shared memory
+template <typename B, typename V, int K>
+__global__ void seg_cost_kernel(const int *__restrict__ segBegin, const int *__restrict__ segEnd,
+                                const int *__restrict__ fragPtr, int numSegs, long long *__restrict__ cost) {
+    int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s > numSegs) return;
+    long long c = 0;
+    if (s < numSegs) {
+        const int f0 = segBegin[s], f1 = segEnd[s];
+        c = (long long)(f1 - f0) * (sizeof(B) + 4 + 4 * K) + (long long)(fragPtr[f1] - fragPtr[f0]) * sizeof(V);
+    }
+    cost[s] = c;
+}
+
+// CTA c starts at the first segment whose byte prefix reaches c * STAGE_BYTES
+template <typename B, typename V, int K>
+__global__ void cta_desc_kernel(const long long *__restrict__ prefix, const int *__restrict__ segBegin,
+                                const int *__restrict__ segEnd, const int *__restrict__ fragPtr, int numSegs,
+                                int numCtas, int STAGE_BYTES, CtaDesc *__restrict__ desc,
+                                unsigned *__restrict__ maxBytes) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= numCtas) return;
+    auto first = [&](int cc) {
+        if (cc >= numCtas) return numSegs;
+        const long long target = (long long)cc * STAGE_BYTES;
+        int lo = 0, hi = numSegs;
+        while (lo < hi) {
+            int mid = (lo + hi) >> 1;
+            if (prefix[mid] < target)
+                lo = mid + 1;
+            else
+                hi = mid;
+        }
+        return lo;
+    };
+    CtaDesc d;
+    d.seg0 = c == 0 ? 0 : first(c);
+    d.seg1 = first(c + 1);
+    d.pad0 = d.pad1 = 0;
+    if (d.seg1 > d.seg0) {
+        d.f0 = segBegin[d.seg0];
+        d.f1 = segEnd[d.seg1 - 1];
+    } else {
+        d.f0 = d.f1 = 0;
+    }
+    d.v0 = fragPtr[d.f0];
+    d.v1 = fragPtr[d.f1];
+    desc[c] = d;
+    atomicMax(maxBytes, StageLayout<B, V, K>(d.f0, d.f1, d.v0, d.v1).total());
 }
 
 }  // namespace
@@ -245,7 +408,50 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     cudaFree(segCount);
     cudaFree(multiCount);
     cudaFree(firstSlot);
-    return e != cudaSuccess ? e : e2;
+    if (e != cudaSuccess) return e;
+    if (e2 != cudaSuccess) return e2;
+    if ((e = cudaMalloc(&P.segDesc, (ns > 0 ? ns : 1) * sizeof(int4))) != cudaSuccess) return e;
+    seg_pack_kernel<<<(P.numSegs + 255) / 256, 256, 0, s>>>(P.segPanel, P.segBegin, P.segEnd, P.segSlot, P.numSegs,
+                                                            (int4 *)P.segDesc);
+    // CTA descriptors of the TMA-staged kernel: consecutive segments grouped by the bytes they stage
+    long long *cost = nullptr, *prefix = nullptr;
+    unsigned *maxBytes = nullptr;
+    if ((e = cudaMalloc(&cost, (ns + 1) * sizeof(long long))) != cudaSuccess) return e;
+    if ((e = cudaMalloc(&prefix, (ns + 1) * sizeof(long long))) != cudaSuccess) return e;
+    if ((e = cudaMalloc(&maxBytes, sizeof(unsigned))) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(maxBytes, 0, sizeof(unsigned), s)) != cudaSuccess) return e;
+    const int cgrid = (P.numSegs + 1 + 255) / 256;
+    if (dtype == MX_FP64)
+        seg_cost_kernel<uint32_t, double, 4><<<cgrid, 256, 0, s>>>(P.segBegin, P.segEnd, P.A.fragPtr, P.numSegs, cost);
+    else
+        seg_cost_kernel<uint64_t, __half, 8><<<cgrid, 256, 0, s>>>(P.segBegin, P.segEnd, P.A.fragPtr, P.numSegs, cost);
+    if ((e = exclusive_sum(tmp, cost, prefix, P.numSegs + 1, s)) != cudaSuccess) return e;
+    long long totalBytes = 0;
+    if ((e = cudaMemcpyAsync(&totalBytes, prefix + P.numSegs, sizeof(long long), cudaMemcpyDeviceToHost, s)) !=
+        cudaSuccess)
+        return e;
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    if (const char *ev = getenv("MX_STAGE_BYTES")) g_stage_bytes = atoi(ev);
+    if (const char *ev = getenv("MX_STAGE_WARPS")) g_stage_warps = atoi(ev) == 4 ? 4 : 8;
+    const int STAGE_BYTES = g_stage_bytes;
+    P.numCtas = (int)((totalBytes + STAGE_BYTES - 1) / STAGE_BYTES);
+    if (P.numCtas < 1) P.numCtas = 1;
+    if ((e = cudaMalloc(&P.ctaDesc, (size_t)P.numCtas * sizeof(CtaDesc))) != cudaSuccess) return e;
+    if (dtype == MX_FP64)
+        cta_desc_kernel<uint32_t, double, 4><<<(P.numCtas + 127) / 128, 128, 0, s>>>(
+            prefix, P.segBegin, P.segEnd, P.A.fragPtr, P.numSegs, P.numCtas, STAGE_BYTES, (CtaDesc *)P.ctaDesc, maxBytes);
+    else
+        cta_desc_kernel<uint64_t, __half, 8><<<(P.numCtas + 127) / 128, 128, 0, s>>>(
+            prefix, P.segBegin, P.segEnd, P.A.fragPtr, P.numSegs, P.numCtas, STAGE_BYTES, (CtaDesc *)P.ctaDesc, maxBytes);
+    unsigned mb = 0;
+    if ((e = cudaMemcpyAsync(&mb, maxBytes, sizeof(unsigned), cudaMemcpyDeviceToHost, s)) != cudaSuccess) return e;
+    e = cudaStreamSynchronize(s);
+    P.stageBytes = (int)mb;
+    cudaFree(cost);
+    cudaFree(prefix);
+    cudaFree(maxBytes);
+    if (e != cudaSuccess) return e;
+    return cudaGetLastError();
 }
 
 void tile_plan_free(TilePlan &P) {
@@ -256,6 +462,10 @@ void tile_plan_free(TilePlan &P) {
     cudaFree(P.panelFirstSeg);
     cudaFree(P.partial);
     cudaFree(P.panelCount);
+    cudaFree(P.ctaDesc);
+    cudaFree(P.segDesc);
+    P.ctaDesc = P.segDesc = nullptr;
+    P.numCtas = 0;
     P.segPanel = P.segBegin = P.segEnd = P.segSlot = P.panelFirstSeg = nullptr;
     P.partial = nullptr;
     P.panelCount = nullptr;
@@ -265,32 +475,37 @@ void tile_plan_free(TilePlan &P) {
 int tile_launches(const TilePlan &P) { return P.numSegs > 0 ? 1 : 0; }
 
 cudaError_t tile_spmv(int dtype, const TilePlan &P, const void *x_d, void *out, const int *row_map, bool out_is_acc,
-                      bool accumulate, int *, cudaStream_t s) {
+                      bool accumulate, int *dev_err, cudaStream_t s) {
     if (P.numSegs <= 0) return cudaSuccess;
-    dim3 grid((P.numSegs + TILE_WARPS - 1) / TILE_WARPS), block(TILE_WARPS * 32);
-#define MX_TILE_ARGS(BT, VT, AT)                                                                                   \
-    (const VT *)x_d, P.A.fragPtr, (const BT *)P.A.fragBit, (const VT *)P.A.tcVal, P.A.AToX, P.segPanel, P.segBegin, P.segEnd, \
-        P.segSlot, P.panelFirstSeg, (AT *)P.partial, P.panelCount
-    if (dtype == MX_FP64) {
-        if (accumulate)
-            tile_kernel_fp64<double, true><<<grid, block, 0, s>>>(MX_TILE_ARGS(uint32_t, double, double),
-                                                                  (double *)out, row_map, P.A.dRows, P.numSegs);
-        else
-            tile_kernel_fp64<double, false><<<grid, block, 0, s>>>(MX_TILE_ARGS(uint32_t, double, double),
-                                                                   (double *)out, row_map, P.A.dRows, P.numSegs);
-    } else {
-        if (out_is_acc)
-            tile_kernel_fp16<float, false><<<grid, block, 0, s>>>(MX_TILE_ARGS(uint64_t, __half, float),
-                                                                  (float *)out, row_map, P.A.dRows, P.numSegs);
-        else if (accumulate)
-            tile_kernel_fp16<__half, true><<<grid, block, 0, s>>>(MX_TILE_ARGS(uint64_t, __half, float),
-                                                                  (__half *)out, row_map, P.A.dRows, P.numSegs);
-        else
-            tile_kernel_fp16<__half, false><<<grid, block, 0, s>>>(MX_TILE_ARGS(uint64_t, __half, float),
-                                                                   (__half *)out, row_map, P.A.dRows, P.numSegs);
+    if (P.ctaDesc && P.stageBytes > 0 && P.stageBytes <= 200 * 1024) {
+        dim3 sg(P.numCtas), sb(g_stage_warps * 32);
+        const size_t smem = (size_t)P.stageBytes;
+#define MX_STAGED(BT, VT, KK, OT, AC, AT)                                                                            \
+    do {                                                                                                             \
+        auto kern = g_stage_warps == 4 ? tile_kernel_staged<BT, VT, KK, OT, AC, 4>                                   \
+                                       : tile_kernel_staged<BT, VT, KK, OT, AC, 8>;                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        kern<<<sg, sb, smem, s>>>((const VT *)x_d, P.A.fragPtr, (const BT *)P.A.fragBit, (const VT *)P.A.tcVal,      \
+                                  P.A.AToX, (const CtaDesc *)P.ctaDesc, (const int4 *)P.segDesc,                     \
+                                  P.panelFirstSeg, (AT *)P.partial, P.panelCount, (OT *)out, row_map, P.A.dRows,     \
+                                  dev_err);                                                                          \
+    } while (0)
+        if (dtype == MX_FP64) {
+            if (accumulate)
+                MX_STAGED(uint32_t, double, 4, double, true, double);
+            else
+                MX_STAGED(uint32_t, double, 4, double, false, double);
+        } else if (out_is_acc) {
+            MX_STAGED(uint64_t, __half, 8, float, false, float);
+        } else if (accumulate) {
+            MX_STAGED(uint64_t, __half, 8, __half, true, float);
+        } else {
+            MX_STAGED(uint64_t, __half, 8, __half, false, float);
+        }
+#undef MX_STAGED
+        return cudaGetLastError();
     }
-#undef MX_TILE_ARGS
-    return cudaGetLastError();
+    return cudaErrorInvalidConfiguration;  // a work segment is at most SEG fragments: its stage always fits
 }
 
 }  // namespace mx
