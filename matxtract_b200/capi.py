@@ -9,7 +9,10 @@ import numpy as np
 FP64, FP16 = 0, 1
 DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
 COLSPACE_AUTO, COLSPACE_PERMUTED, COLSPACE_ORIGINAL = 0, 1, 2
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
+import os
+
+# MATXTRACT_B200_LIB points at another build of the same library (e.g. one compiled with different tile constants)
+_LIB_PATH = Path(os.environ.get("MATXTRACT_B200_LIB", Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"))
 
 STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
           6: "MX_ERR_TIMEOUT", 7: "MX_ERR_NOMEM", 8: "MX_ERR_NO_DEVICE", 9: "MX_ERR_TOO_LARGE"}

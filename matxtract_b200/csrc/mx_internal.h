@@ -12,16 +12,25 @@ namespace mx {
 
 // ------------------------------------------------------------------------------------------------
 // Residual CSR kernel geometry: a tile is RESID_THREADS * IPT consecutive non-zeros.
-constexpr int RESID_THREADS = 256;
+#ifndef MX_RESID_THREADS
+#define MX_RESID_THREADS 128
+#endif
+#ifndef MX_RESID_IPT_FP64
+#define MX_RESID_IPT_FP64 8
+#endif
+#ifndef MX_RESID_IPT_FP16
+#define MX_RESID_IPT_FP16 16
+#endif
+constexpr int RESID_THREADS = MX_RESID_THREADS;
 template <typename V>
 struct ResidCfg;
 template <>
 struct ResidCfg<double> {
-    static constexpr int IPT = 8;
+    static constexpr int IPT = MX_RESID_IPT_FP64;
 };
 template <>
 struct ResidCfg<__half> {
-    static constexpr int IPT = 16;
+    static constexpr int IPT = MX_RESID_IPT_FP16;
 };
 
 // Device error word bits.
