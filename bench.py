@@ -322,6 +322,12 @@ def run_ours(args):
     else:
         dom, dom_ms, dom_bytes = "resid_kernel(+fixup)", halves["ms_resid"], b_resid
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    # DRAM read + write bytes of the dominant kernel per launch, from the ncu captures summarised under profiles/
+    # (resid_kernel_c2_fp16.md, tile_and_resid_kernels_c3_fp64.md); null for workloads that were not captured
+    traffic = None
+    if world == 1 and not args.n and not args.tau:
+        traffic = {("c2", "resid_kernel(+fixup)"): 137.4e6, ("c3", "resid_kernel(+fixup)"): 643.1e6,
+                   ("c3", "tile_kernel"): 479.4e6}.get((cfg.name, dom))
     eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
 
     def shutdown():
@@ -368,7 +374,7 @@ def run_ours(args):
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms,
         "ms_tile_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                      "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": n_total * vb,
                 "d2h_bytes_per_step": n_total * vb},
