@@ -100,8 +100,13 @@ def workload_matrix(args, rank, world):
     from matxtract_b200 import synth
 
     cfg = synth.CONFIGS[args.workload]
-    n_local = args.n or cfg.n
-    n_total = n_local * world
+    if args.scaling == "strong":  # the whole matrix is fixed, every rank owns n/world rows
+        n_total = args.n or cfg.n
+        n_local = n_total // world
+        n_total = n_local * world
+    else:  # weak: every rank owns a slab of the configuration's size
+        n_local = args.n or cfg.n
+        n_total = n_local * world
     m = synth.generate(cfg, n=n_total, rows=(rank * n_local, (rank + 1) * n_local))
     return cfg, n_local, n_total, m
 
@@ -358,7 +363,7 @@ def run_ours(args):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f64" if dtype == mx.FP64 else "f16", "data": "synthetic",
         "config": {"workload": describe(cfg, n_local, world), "tau": list(tau), "n": n_total, "nnz": nnz_total,
                    "l2": "no flush: the matrix streamed per step is larger than the 126 MB L2"
@@ -396,6 +401,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: weak = --n rows per GPU (default), strong = --n rows in total, split over the GPUs")
     ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr"], help="executor of the core-dense block")
     ap.add_argument("--colspace", default="auto", choices=["auto", "permuted", "original"],
                     help="column numbering used for execution")
