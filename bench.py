@@ -252,9 +252,35 @@ def run_ours(args):
         y_work = torch.zeros(n_local, dtype=tdt, device=f"cuda:{local}")
     stream.synchronize()
 
+    # N > 1: y is assembled either by the kernels themselves (rows stored into every GPU's peer-mapped y over NVLink,
+    # one barrier afterwards) or by an NCCL all-gather after the kernels
+    peer_y = None
+    gather = "none"
+    if world > 1:
+        gather = "nccl all-gather"
+        if args.gather in ("auto", "fused"):
+            try:
+                from matxtract_b200.distributed import PeerY
+
+                with torch.cuda.stream(stream):
+                    peer_y = PeerY(n_total, tdt, torch.device("cuda", local))
+                gather = "fused into the SpMV epilogue (peer stores over NVLink + barrier)"
+            except Exception as e:  # symmetric memory unavailable: keep the NCCL path
+                if args.gather == "fused":
+                    raise
+                peer_y = None
+                gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
+    last_y = [y_full]
+
     def step_device():
         if world == 1:
             h.spmv(x_dev, y_full)
+        elif peer_y is not None:
+            buf, ptrs = peer_y.next()
+            h.spmv_peers(x_dev, ptrs, rank * n_local)
+            with torch.cuda.stream(stream):
+                peer_y.finish()
+            last_y[0] = buf
         else:
             h.spmv(x_dev, y_work)
             with torch.cuda.stream(stream):
@@ -265,7 +291,7 @@ def run_ours(args):
             x_dev.copy_(x_host, non_blocking=True)
         step_device()
         with torch.cuda.stream(stream):
-            y_host.copy_(y_full, non_blocking=True)
+            y_host.copy_(last_y[0], non_blocking=True)
         stream.synchronize()
 
     def barrier():
@@ -337,8 +363,10 @@ def run_ours(args):
 
     def shutdown():
         # torch tensors that lived on the handle's stream must go before the stream does
-        nonlocal x_dev, y_full, y_work, x_host, y_host
+        nonlocal x_dev, y_full, y_work, x_host, y_host, peer_y
         stream.synchronize()
+        last_y[0] = None
+        peer_y = None
         del x_dev, y_full, y_work, x_host, y_host  # pinned buffers record events on the stream when freed
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
@@ -368,7 +396,7 @@ def run_ours(args):
         "config": {"workload": describe(cfg, n_local, world), "tau": list(tau), "n": n_total, "nnz": nnz_total,
                    "l2": "no flush: the matrix streamed per step is larger than the 126 MB L2"
                    if b_alg_total / world > 126e6 else "matrix smaller than L2: latency figure, not a bandwidth figure",
-                   "parallelism": f"rows x{world}, x replicated, y all-gather (NCCL)" if world > 1 else "1 GPU"},
+                   "parallelism": f"rows x{world}, x replicated, y: {gather}" if world > 1 else "1 GPU"},
         "effective_gbs": eff_gbs, "pct_of_8tbs": 100.0 * eff_gbs / NOMINAL_HBM_GBS / world,
         "pct_of_measured_hbm": 100.0 * eff_gbs / peak / world,
         "algorithmic_bytes_per_step": b_alg_total,
@@ -401,6 +429,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: how y is assembled (auto = fused peer stores when symmetric memory is available)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: weak = --n rows per GPU (default), strong = --n rows in total, split over the GPUs")
     ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr"], help="executor of the core-dense block")

@@ -98,6 +98,14 @@ int mx_download_partition(mx_handle_t h, const mx_partition_arrays *out);
  * second produces the final y, so there is no merge pass and no host scatter
  * (replaces test/test_autotc_spmv.cpp:1507-1559). */
 int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev);
+/* Row-partitioned product across the GPUs of one box with the y all-gather fused into the kernel (the reference is
+ * single-GPU; this is the multi-GPU exchange step).  This handle owns the row slab [row_offset, row_offset + n_rows)
+ * of the whole matrix; y_peers[g] is a DEVICE pointer, valid on this GPU, to the full-length y of GPU g (peer-mapped
+ * memory, e.g. a symmetric-memory buffer; y_peers must include this GPU's own buffer; n_peers <= 8).  Every finished
+ * row is stored into all n_peers buffers with plain stores over NVLink while the rest of the kernel is still
+ * computing.  The caller runs a barrier across the GPUs afterwards (every y is complete once all GPUs have passed it);
+ * nothing in the kernels waits on another GPU. */
+int mx_spmv_peers(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, long long row_offset);
 /* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
 /* Timing loop on the device: `warm` untimed and `iters` timed repetitions (the reference uses 200 and

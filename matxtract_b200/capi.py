@@ -63,6 +63,7 @@ SYMBOLS = {
     "mx_download_partition": (_i, [_vp, C.POINTER(_PartitionArrays)]),
     "mx_spmv": (_i, [_vp, _vp, _vp]),
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
+    "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_spmv_launches": (_i, [_vp]),
     "mx_set_dd_executor": (_i, [_vp, _i]),
@@ -130,6 +131,7 @@ class MatXtract:
             raise MxError(st, lib().mx_status_string(st).decode())
         self.n_rows = self.n_cols = self.nnz = 0
         self.stats = None
+        self._peer_arrays = {}
 
     def _ck(self, st):
         if st != 0:
@@ -178,6 +180,14 @@ class MatXtract:
     def spmv(self, x_dev, y_dev):
         """x_dev / y_dev: device pointers (ints) or torch CUDA tensors; asynchronous on ``self.stream``."""
         self._ck(lib().mx_spmv(self._h, _ptr(x_dev), _ptr(y_dev)))
+
+    def spmv_peers(self, x_dev, peer_ptrs, row_offset: int):
+        """Rows of this slab are stored into every GPU's full-length y (peer_ptrs: device addresses as ints)."""
+        key = tuple(peer_ptrs)
+        arr = self._peer_arrays.get(key)
+        if arr is None:
+            arr = self._peer_arrays[key] = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        self._ck(lib().mx_spmv_peers(self._h, _ptr(x_dev), arr, len(peer_ptrs), int(row_offset)))
 
     def spmv_host(self, x: np.ndarray, y: np.ndarray | None = None) -> np.ndarray:
         x = _c(x, np_dtype(self.dtype))

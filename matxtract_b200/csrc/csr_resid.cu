@@ -47,8 +47,10 @@ __device__ __forceinline__ void from_acc(float a, __half *o) { *o = __float2half
 enum OutMode : int {
     OUT_Y = 0,        // y[r] = sum (+ tile contribution of hot rows)
     OUT_Y_ACCUM = 1,  // y[r] += sum  (the reference's cdspmv adds into y, cdSpMV.cu:418,483)
-    OUT_CARRIER = 2   // carrier[row_map[r]] = sum in the accumulate type (core-dense block run as CSR)
+    OUT_CARRIER = 2,  // carrier[row_map[r]] = sum in the accumulate type (core-dense block run as CSR)
+    OUT_Y_PEERS = 3   // y_peer[g][row_offset + r] = sum for every GPU g of the box: the y all-gather, fused
 };
+constexpr int MAX_PEERS = 8;
 
 // tile_row[t] = number of (non-empty) rows whose end lies at or before the first non-zero of tile t
 __global__ void tile_row_kernel(const int *__restrict__ cPtr, int m_rows, int nnz, int tile_nnz, int num_tiles,
@@ -96,6 +98,9 @@ struct RowOut {
     const A *__restrict__ ytile;           // HAS_TILE: tile-half contribution per row
     const uint32_t *__restrict__ hotmask;  // HAS_TILE: bit r set when row r has one
     const int *__restrict__ nzRow;         // k-th non-empty row -> row index (null: no empty rows, identity)
+    V *peer_y[MAX_PEERS];                  // OUT_Y_PEERS: every GPU's full-length y (peer-mapped), this GPU's included
+    int n_peers;
+    long long row_offset;                  // OUT_Y_PEERS: first row of this GPU's slab in the full y
 };
 
 template <typename V, bool HAS_TILE, int MODE>
@@ -108,6 +113,14 @@ __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename Ac
         if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
     }
     if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
+    if (MODE == OUT_Y_PEERS) {
+        // plain stores into every GPU's y over NVLink: consecutive rows of a warp make contiguous segments, and the
+        // traffic overlaps the rest of the kernel (which is bound by x gathers, not by NVLink)
+#pragma unroll
+        for (int g = 0; g < MAX_PEERS; ++g)
+            if (g < o.n_peers) from_acc(v, o.peer_y[g] + o.row_offset + r);
+        return;
+    }
     from_acc(v, o.y + r);
 }
 
@@ -310,7 +323,8 @@ __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ p
 
 template <typename V>
 cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void *ytile, const uint32_t *hotmask,
-                         int mode, const int *row_map, cudaStream_t s) {
+                         int mode, const int *row_map, cudaStream_t s, void *const *peers = nullptr, int n_peers = 0,
+                         long long row_offset = 0) {
     using A = typename AccOf<V>::T;
     constexpr int IPT = ResidCfg<V>::IPT;
     const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
@@ -321,6 +335,9 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     out.ytile = (const A *)ytile;
     out.hotmask = hotmask;
     out.nzRow = P.nz_row;
+    out.n_peers = n_peers;
+    out.row_offset = row_offset;
+    for (int g = 0; g < MAX_PEERS; ++g) out.peer_y[g] = g < n_peers ? (V *)peers[g] : nullptr;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
     const int fgrid = (fwork + 127) / 128;
@@ -335,6 +352,10 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     } while (0)
     if (mode == OUT_CARRIER)
         MX_LAUNCH(false, OUT_CARRIER);
+    else if (mode == OUT_Y_PEERS && hasTile)
+        MX_LAUNCH(true, OUT_Y_PEERS);
+    else if (mode == OUT_Y_PEERS)
+        MX_LAUNCH(false, OUT_Y_PEERS);
     else if (hasTile && mode == OUT_Y_ACCUM)
         MX_LAUNCH(true, OUT_Y_ACCUM);
     else if (hasTile)
@@ -410,6 +431,14 @@ cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, co
     const int mode = accumulate ? OUT_Y_ACCUM : OUT_Y;
     if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, mode, nullptr, s);
     return resid_spmv_t<__half>(P, x, y, ytile, hotmask, mode, nullptr, s);
+}
+
+cudaError_t resid_spmv_peers(int dtype, const ResidPlan &P, const void *x, void *const *peers, int n_peers,
+                             long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s) {
+    if (n_peers < 1 || n_peers > MAX_PEERS) return cudaErrorInvalidValue;
+    if (dtype == MX_FP64)
+        return resid_spmv_t<double>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, peers, n_peers, row_offset);
+    return resid_spmv_t<__half>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, peers, n_peers, row_offset);
 }
 
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, void *carrier, const int *row_map,

@@ -221,7 +221,20 @@ static cudaError_t dd_enqueue(mx_handle_t h, const void *x) {
 }
 
 static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid,
-                        bool permute = true) {
+                        bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0) {
+    if (peers) {  // final rows go to every GPU's y
+        const void *x = x_dev;
+        if (h->stats.active) {
+            if (!h->use_orig_cols) {
+                HCK(gather_vector(h->dtype, x_dev, h->part.xperm, h->x_perm, h->n_cols, h->stream));
+                x = h->x_perm;
+            }
+            HCK(dd_enqueue(h, x));
+        }
+        HCK(resid_spmv_peers(h->dtype, h->resid, x, peers, n_peers, row_offset, h->stats.active ? h->ytile : nullptr,
+                             h->stats.active ? h->part.hotmask : nullptr, h->stream));
+        return MX_OK;
+    }
     if (h->stats.active) {
         const void *x = x_dev;
         if (!h->use_orig_cols) {
@@ -405,6 +418,15 @@ int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev) {
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv: call mx_partition first");
     HCK(cudaSetDevice(h->device));
     return spmv_enqueue(h, x_dev, y_dev, true, true);
+}
+
+int mx_spmv_peers(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, long long row_offset) {
+    if (!h || !x_dev || !y_peers || n_peers < 1 || n_peers > 8 || row_offset < 0) return MX_ERR_INVALID;
+    for (int g = 0; g < n_peers; ++g)
+        if (!y_peers[g]) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_peers: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    return spmv_enqueue(h, x_dev, nullptr, true, true, true, y_peers, n_peers, row_offset);
 }
 
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {

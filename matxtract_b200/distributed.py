@@ -50,6 +50,37 @@ def all_gather_rows(y_local, bounds, group=None):
     return torch.cat([out[g * longest: g * longest + sizes[g]] for g in range(world)])
 
 
+class PeerY:
+    """Full-length y of every GPU, mapped into every other GPU (torch symmetric memory over NVLink), double-buffered.
+
+    ``mx_spmv_peers`` stores this rank's rows into all of them from inside the SpMV kernels; ``finish()`` is the one
+    barrier after which every rank's y is complete.  Two buffers alternate so that a rank that is still reading the
+    previous product (in stream order) is never overwritten by a faster peer's next product.
+    """
+
+    def __init__(self, n_total, torch_dtype, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = dist.group.WORLD if group is None else group
+        self.bufs, self.hdls = [], []
+        for _ in range(2):
+            t = symm_mem.empty(n_total, dtype=torch_dtype, device=device)
+            self.bufs.append(t)
+            self.hdls.append(symm_mem.rendezvous(t, group))
+        self.ptrs = [list(h.buffer_ptrs) for h in self.hdls]
+        self.k = 0
+
+    def next(self):
+        """(tensor that will hold the next product, device addresses of that buffer on every GPU)."""
+        self.k ^= 1
+        return self.bufs[self.k], self.ptrs[self.k]
+
+    def finish(self):
+        """Barrier across the GPUs on the current stream: afterwards the buffer returned by next() is complete."""
+        self.hdls[self.k].barrier(channel=0)
+
+
 class DistributedSpMV:
     """This rank's slab on its GPU plus the collective that assembles y.
 
@@ -58,7 +89,7 @@ class DistributedSpMV:
     """
 
     def __init__(self, dtype, n_cols, row_ptr, col_ind, val, rank, world, tau=(0.0, 0.0), device=None, balance="nnz",
-                 local_spmv=None, group=None):
+                 local_spmv=None, group=None, fused=False):
         self.rank, self.world, self.group = rank, world, group
         n = len(row_ptr) - 1
         self.bounds = nnz_balanced_bounds(row_ptr, world) if balance == "nnz" else equal_row_bounds(n, world)
@@ -80,6 +111,8 @@ class DistributedSpMV:
             self.stream = torch.cuda.ExternalStream(self.handle.stream, device=self.device)
             tdt = torch.float64 if dtype == 0 else torch.float16
             self._y = torch.zeros(max(self.rows, 1), dtype=tdt, device=self.device)[: self.rows]
+            # fused: the kernels store y rows straight into every GPU's y (peer-mapped), one barrier afterwards
+            self.peer_y = PeerY(n, tdt, self.device, group) if fused else None
         else:
             self._slab = (rp, ci, v)
 
@@ -90,6 +123,12 @@ class DistributedSpMV:
         if self._local is not None:
             y_local = self._local(self._slab, x_full)
             return all_gather_rows(y_local, self.bounds, self.group)
+        if self.peer_y is not None:
+            y, ptrs = self.peer_y.next()
+            self.handle.spmv_peers(x_full, ptrs, self.bounds[self.rank])
+            with torch.cuda.stream(self.stream):
+                self.peer_y.finish()
+            return y
         self.handle.spmv(x_full, self._y)
         with torch.cuda.stream(self.stream):
             return all_gather_rows(self._y, self.bounds, self.group)
@@ -100,6 +139,7 @@ class DistributedSpMV:
 
             self.stream.synchronize()
             self._y = None
+            self.peer_y = None
             torch.cuda.synchronize()
             self.handle.close()
             self.handle = None
