@@ -271,13 +271,22 @@ def run_ours(args):
                 peer_y = None
                 gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
     last_y = [y_full]
+    method = ["epilogue"]  # with peer buffers: "epilogue" (rows stored to all peers by the kernels) or "push"
+    push_table = torch.zeros(8, dtype=torch.int64, device=f"cuda:{local}") if world > 1 else None
 
     def step_device():
         if world == 1:
             h.spmv(x_dev, y_full)
-        elif peer_y is not None:
+        elif peer_y is not None and method[0] == "epilogue":
             buf, ptrs = peer_y.next()
             h.spmv_peers(x_dev, ptrs, rank * n_local)
+            with torch.cuda.stream(stream):
+                peer_y.finish()
+            last_y[0] = buf
+        elif peer_y is not None and method[0] == "push":
+            buf, ptrs = peer_y.next()
+            h.spmv(x_dev, buf[rank * n_local: (rank + 1) * n_local])
+            h.peer_push(ptrs, rank, rank * n_local, n_local, push_table)
             with torch.cuda.stream(stream):
                 peer_y.finish()
             last_y[0] = buf
@@ -329,6 +338,26 @@ def run_ours(args):
         dist.all_reduce(t)
         nnz_total = int(t.item())
 
+    if world > 1 and peer_y is not None and args.gather == "auto":
+        # pick the fastest way of assembling y for this workload (all ranks agree: the times are max-reduced)
+        trial = {}
+        for mth in ("epilogue", "push", "nccl"):
+            saved = peer_y
+            if mth == "nccl":
+                peer_y = None
+            else:
+                method[0] = mth
+            trial[mth] = timed(step_device, 30, 5)
+            peer_y = saved
+        best = min(trial, key=trial.get)
+        if best == "nccl":
+            peer_y = None
+            gather = "nccl all-gather"
+        else:
+            method[0] = best
+            gather = ("fused into the SpMV epilogue (peer stores over NVLink + barrier)" if best == "epilogue"
+                      else "peer push kernel (16-byte stores over NVLink + barrier)")
+        gather += " [auto: " + ", ".join(f"{k} {v * 1e3:.0f} us" for k, v in trial.items()) + "]"
     ms_step = timed(step_device, args.steps, max(3, args.warmup))
     value = 2.0 * nnz_total / (ms_step * 1e-3) / 1e9
     ms_e2e = timed(step_e2e, max(10, args.steps // 10), 3)
@@ -363,10 +392,11 @@ def run_ours(args):
 
     def shutdown():
         # torch tensors that lived on the handle's stream must go before the stream does
-        nonlocal x_dev, y_full, y_work, x_host, y_host, peer_y
+        nonlocal x_dev, y_full, y_work, x_host, y_host, peer_y, push_table
         stream.synchronize()
         last_y[0] = None
         peer_y = None
+        push_table = None
         del x_dev, y_full, y_work, x_host, y_host  # pinned buffers record events on the stream when freed
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
@@ -421,13 +451,14 @@ def run_ours(args):
 
 
 def main():
-    ap = argparse.ArgumentParser()
+    ap = argparse.ArgumentParser(allow_abbrev=False)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--n", type=int, default=0, help="rows per GPU (default: the configuration's size)")
+    ap.add_argument("--n", "--rows", dest="n", type=int, default=0,
+                    help="rows per GPU (default: the configuration's size); spell it --rows under torchrun")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: how y is assembled (auto = fused peer stores when symmetric memory is available)")

@@ -106,6 +106,12 @@ int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev);
  * computing.  The caller runs a barrier across the GPUs afterwards (every y is complete once all GPUs have passed it);
  * nothing in the kernels waits on another GPU. */
 int mx_spmv_peers(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, long long row_offset);
+/* The unfused alternative for small slabs: after mx_spmv wrote this GPU's rows into its own full-length y
+ * (y_peers[self] + row_offset), copy those rows into the same place of every other GPU's y with 16-byte peer stores.
+ * table_dev: 64 bytes of device memory the call may use (the peers' row addresses).  Followed, like mx_spmv_peers, by
+ * the caller's barrier across the GPUs. */
+int mx_peer_push(int dtype, void *const *y_peers, int n_peers, int self, long long row_offset, long long n_rows,
+                 void *table_dev, void *stream);
 /* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
 /* Timing loop on the device: `warm` untimed and `iters` timed repetitions (the reference uses 200 and

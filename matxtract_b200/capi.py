@@ -64,6 +64,7 @@ SYMBOLS = {
     "mx_spmv": (_i, [_vp, _vp, _vp]),
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
+    "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_spmv_launches": (_i, [_vp]),
     "mx_set_dd_executor": (_i, [_vp, _i]),
@@ -188,6 +189,15 @@ class MatXtract:
         if arr is None:
             arr = self._peer_arrays[key] = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
         self._ck(lib().mx_spmv_peers(self._h, _ptr(x_dev), arr, len(peer_ptrs), int(row_offset)))
+
+    def peer_push(self, peer_ptrs, self_rank: int, row_offset: int, n_rows: int, table_dev):
+        """Copies this GPU's rows of y (already in its own full-length buffer) to every other GPU's buffer."""
+        key = tuple(peer_ptrs)
+        arr = self._peer_arrays.get(key)
+        if arr is None:
+            arr = self._peer_arrays[key] = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        _raise(lib().mx_peer_push(self.dtype, arr, len(peer_ptrs), self_rank, int(row_offset), int(n_rows),
+                                  _ptr(table_dev), C.c_void_p(self.stream)))
 
     def spmv_host(self, x: np.ndarray, y: np.ndarray | None = None) -> np.ndarray:
         x = _c(x, np_dtype(self.dtype))

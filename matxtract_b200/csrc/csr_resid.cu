@@ -19,6 +19,7 @@
 //      began earlier); a second tiny kernel adds them in tile order.
 // Every row of y is stored exactly once; rows that also have a tile-kernel contribution (flagged in
 // `hotmask`) add it at that point, so there is no merge pass.
+#include <algorithm>
 #include <climits>
 
 #include "device_prims.cuh"
@@ -315,6 +316,20 @@ __global__ void map_indices_kernel(const int *__restrict__ in, const int *__rest
     if (i < n) out[i] = __ldg(map + __ldg(in + i));
 }
 
+// this GPU's finished slab -> the same rows of every other GPU's y (16-byte peer stores over NVLink)
+__global__ void peer_push_kernel(const int4 *__restrict__ src, int4 *const *__restrict__ dst_table, long long n16,
+                                 int n_dst) {
+    int4 *dst = dst_table[blockIdx.y];
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) dst[i] = __ldg(src + i);
+}
+__global__ void peer_push_bytes_kernel(const unsigned char *__restrict__ src, unsigned char *const *__restrict__ dst_table,
+                                       long long nbytes) {
+    unsigned char *dst = dst_table[blockIdx.y];
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += stride) dst[i] = src[i];
+}
+
 template <typename V>
 __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ perm, V *__restrict__ out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -599,5 +614,44 @@ extern "C" int mx_csr_spmv_static(int dtype, int n_rows, int n_cols, int nnz, co
                         : resid_spmv_t<__half>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s);
     STCK(e);
 #undef STCK
+    return MX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Slab push: after a product that wrote this GPU's rows into its own full-length y, copy those rows into the same
+// place of every other GPU's y.  dst_table is a small device array of the peers' row addresses (filled by the caller
+// side below with cudaMemcpyAsync from a host array that lives until the copy has been issued).
+// ---------------------------------------------------------------------------------------------------------------
+extern "C" int mx_peer_push(int dtype, void *const *y_peers, int n_peers, int self, long long row_offset,
+                            long long n_rows, void *table_dev, void *stream) {
+    using namespace mx;
+    if ((dtype != MX_FP64 && dtype != MX_FP16) || !y_peers || n_peers < 1 || n_peers > MAX_PEERS || self < 0 ||
+        self >= n_peers || row_offset < 0 || n_rows < 0 || !table_dev)
+        return MX_ERR_INVALID;
+    if (n_peers == 1 || n_rows == 0) return MX_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t vb = val_bytes(dtype);
+    unsigned char *host_tab[MAX_PEERS];
+    int nd = 0;
+    for (int g = 0; g < n_peers; ++g)
+        if (g != self) host_tab[nd++] = static_cast<unsigned char *>(y_peers[g]) + (size_t)row_offset * vb;
+    // pageable source: the runtime stages it before returning, so the stack array may go out of scope
+    if (cudaMemcpyAsync(table_dev, host_tab, sizeof(void *) * nd, cudaMemcpyHostToDevice, s) != cudaSuccess) {
+        cudaGetLastError();
+        return MX_ERR_CUDA;
+    }
+    const unsigned char *src = static_cast<const unsigned char *>(y_peers[self]) + (size_t)row_offset * vb;
+    const long long nbytes = n_rows * (long long)vb;
+    if (((uintptr_t)src & 15) == 0 && (nbytes & 15) == 0) {
+        const long long n16 = nbytes / 16;
+        int gx = (int)std::min<long long>((n16 + 255) / 256, 148 * 4 / nd + 1);
+        peer_push_kernel<<<dim3(gx, nd), 256, 0, s>>>(reinterpret_cast<const int4 *>(src),
+                                                      reinterpret_cast<int4 *const *>(table_dev), n16, nd);
+    } else {
+        int gx = (int)std::min<long long>((nbytes + 255) / 256, 148 * 4 / nd + 1);
+        peer_push_bytes_kernel<<<dim3(gx, nd), 256, 0, s>>>(src, reinterpret_cast<unsigned char *const *>(table_dev),
+                                                            nbytes);
+    }
+    if (cudaGetLastError() != cudaSuccess) return MX_ERR_CUDA;
     return MX_OK;
 }
