@@ -113,6 +113,8 @@ class DistributedSpMV:
             self._y = torch.zeros(max(self.rows, 1), dtype=tdt, device=self.device)[: self.rows]
             # fused: the kernels store y rows straight into every GPU's y (peer-mapped), one barrier afterwards
             self.peer_y = PeerY(n, tdt, self.device, group) if fused else None
+            self.fused = fused  # False (NCCL all-gather), True / "epilogue" (kernels store to all peers), "push"
+            self._table = torch.zeros(8, dtype=torch.int64, device=self.device)
         else:
             self._slab = (rp, ci, v)
 
@@ -125,7 +127,12 @@ class DistributedSpMV:
             return all_gather_rows(y_local, self.bounds, self.group)
         if self.peer_y is not None:
             y, ptrs = self.peer_y.next()
-            self.handle.spmv_peers(x_full, ptrs, self.bounds[self.rank])
+            r0 = self.bounds[self.rank]
+            if self.fused == "push":  # product into this GPU's own y, then 16-byte peer stores of the slab
+                self.handle.spmv(x_full, y[r0: r0 + self.rows])
+                self.handle.peer_push(ptrs, self.rank, r0, self.rows, self._table)
+            else:
+                self.handle.spmv_peers(x_full, ptrs, r0)
             with torch.cuda.stream(self.stream):
                 self.peer_y.finish()
             return y
@@ -140,6 +147,7 @@ class DistributedSpMV:
             self.stream.synchronize()
             self._y = None
             self.peer_y = None
+            self._table = None
             torch.cuda.synchronize()
             self.handle.close()
             self.handle = None
