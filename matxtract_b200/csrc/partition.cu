@@ -35,17 +35,20 @@ template <typename T>
 cudaError_t dalloc(T **p, size_t n) {
     return cudaMalloc((void **)p, (n > 0 ? n : 1) * sizeof(T));
 }
-// scratch buffers of one run, released on every exit path
+// scratch buffers of one run, taken from the stream-ordered pool (no device-wide synchronisation per buffer) and
+// released on every exit path
 struct Scratch {
+    cudaStream_t s;
     std::vector<void *> bufs;
+    explicit Scratch(cudaStream_t stream) : s(stream) {}
     template <typename T>
     cudaError_t alloc(T **p, size_t n) {
-        cudaError_t e = dalloc(p, n);
+        cudaError_t e = cudaMallocAsync((void **)p, (n > 0 ? n : 1) * sizeof(T), s);
         if (e == cudaSuccess) bufs.push_back(*p);
         return e;
     }
     ~Scratch() {
-        for (void *b : bufs) cudaFree(b);
+        for (void *b : bufs) cudaFreeAsync(b, s);
     }
 };
 
@@ -262,7 +265,7 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
     constexpr int K = sizeof(B) == 8 ? 8 : 4;
     *status = MX_OK;
     TempBuf tmp;
-    Scratch sc;
+    Scratch sc(s);
     const int chunkNum = (dRows + 7) / 8;
     T.dRows = dRows;
     T.chunkNum = chunkNum;
@@ -326,7 +329,7 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     *status = MX_OK;
     const int R = A.n_rows, C = A.n_cols, nnz = A.nnz;
     TempBuf tmp;
-    Scratch sc;
+    Scratch sc(s);
     int *colCnt = nullptr, *iota = nullptr, *sortedCnt = nullptr, *colOrder = nullptr, *pref = nullptr, *cut = nullptr,
         *rankOf = nullptr, *isS = nullptr, *sidx = nullptr, *colMap = nullptr, *rowCntD = nullptr,
         *sortedRCnt = nullptr, *rowOrder = nullptr, *hotPos = nullptr, *resLen = nullptr, *Kdd = nullptr,
