@@ -392,8 +392,8 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &P, cudaStream_t s) {
     // rows without entries leave the kernel's row space: cPtr = row pointers of the non-empty rows
     int *flag = nullptr, *pos = nullptr;
     const size_t nr = (size_t)P.n_rows + 1;
-    if ((e = cudaMalloc(&flag, nr * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&pos, nr * sizeof(int))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&flag, nr * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&pos, nr * sizeof(int), s)) != cudaSuccess) return e;
     nonempty_flag_kernel<<<(int)((nr + 255) / 256), 256, 0, s>>>(P.row_ptr, P.n_rows, flag);
     {
         TempBuf tmp;
@@ -408,32 +408,32 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &P, cudaStream_t s) {
         P.nz_row = nullptr;
         P.empty_row = nullptr;
     } else {
-        if ((e = cudaMalloc(&P.c_ptr_own, ((size_t)P.m_rows + 1) * sizeof(int))) != cudaSuccess) return e;
-        if ((e = cudaMalloc(&P.nz_row, ((size_t)P.m_rows + 1) * sizeof(int))) != cudaSuccess) return e;
-        if ((e = cudaMalloc(&P.empty_row, (size_t)P.n_empty * sizeof(int))) != cudaSuccess) return e;
+        if ((e = cudaMallocAsync(&P.c_ptr_own, ((size_t)P.m_rows + 1) * sizeof(int), s)) != cudaSuccess) return e;
+        if ((e = cudaMallocAsync(&P.nz_row, ((size_t)P.m_rows + 1) * sizeof(int), s)) != cudaSuccess) return e;
+        if ((e = cudaMallocAsync(&P.empty_row, (size_t)P.n_empty * sizeof(int), s)) != cudaSuccess) return e;
         compress_rows_kernel<<<(P.n_rows + 255) / 256, 256, 0, s>>>(P.row_ptr, pos, P.n_rows, P.c_ptr_own, P.nz_row,
                                                                     P.empty_row);
         P.c_ptr = P.c_ptr_own;
     }
-    if ((e = cudaMalloc(&P.tile_row, sizeof(int) * (size_t)(P.num_tiles + 1))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.carry, acc_bytes(dtype) * (size_t)P.num_tiles)) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.head, acc_bytes(dtype) * (size_t)P.num_tiles)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.tile_row, sizeof(int) * (size_t)(P.num_tiles + 1), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.carry, acc_bytes(dtype) * (size_t)P.num_tiles, s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.head, acc_bytes(dtype) * (size_t)P.num_tiles, s)) != cudaSuccess) return e;
     tile_row_kernel<<<(P.num_tiles + 1 + 255) / 256, 256, 0, s>>>(P.c_ptr, P.m_rows, P.nnz, P.tile_nnz, P.num_tiles,
                                                                   P.tile_row);
     e = cudaGetLastError();
     cudaError_t e2 = cudaStreamSynchronize(s);
-    cudaFree(flag);
-    cudaFree(pos);
+    if (flag) cudaFreeAsync(flag, s);
+    if (pos) cudaFreeAsync(pos, s);
     return e != cudaSuccess ? e : e2;
 }
 
-void resid_plan_free(ResidPlan &P) {
-    cudaFree(P.tile_row);
-    cudaFree(P.carry);
-    cudaFree(P.head);
-    cudaFree(P.c_ptr_own);
-    cudaFree(P.nz_row);
-    cudaFree(P.empty_row);
+void resid_plan_free(ResidPlan &P, cudaStream_t s) {
+    if (P.tile_row) cudaFreeAsync(P.tile_row, s);
+    if (P.carry) cudaFreeAsync(P.carry, s);
+    if (P.head) cudaFreeAsync(P.head, s);
+    if (P.c_ptr_own) cudaFreeAsync(P.c_ptr_own, s);
+    if (P.nz_row) cudaFreeAsync(P.nz_row, s);
+    if (P.empty_row) cudaFreeAsync(P.empty_row, s);
     P.tile_row = P.c_ptr_own = P.nz_row = P.empty_row = nullptr;
     P.c_ptr = nullptr;
     P.carry = P.head = nullptr;

@@ -58,15 +58,14 @@ struct mx_handle_s {
 namespace {
 
 void drop_plan(mx_handle_t h) {
-    resid_plan_free(h->resid);
-    resid_plan_free(h->ddcsr);
-    tile_plan_free(h->tile);
-    part_arrays_free(h->part);
-    cudaFree(h->ytile);
-    cudaFree(h->x_perm);
-    cudaFree(h->colInd_CD_orig);
-    cudaFree(h->colInd_dd_orig);
-    cudaFree(h->AToX_orig);
+    cudaStream_t s = h->stream;  // frees are ordered after whatever the stream still has in flight
+    resid_plan_free(h->resid, s);
+    resid_plan_free(h->ddcsr, s);
+    tile_plan_free(h->tile, s);
+    part_arrays_free(h->part, s);
+    void *bufs[] = {h->ytile, h->x_perm, h->colInd_CD_orig, h->colInd_dd_orig, h->AToX_orig};
+    for (void *b : bufs)
+        if (b) cudaFreeAsync(b, s);
     h->colInd_CD_orig = h->colInd_dd_orig = h->AToX_orig = nullptr;
     h->use_orig_cols = false;
     h->ytile = h->x_perm = nullptr;
@@ -76,11 +75,9 @@ void drop_plan(mx_handle_t h) {
 
 void drop_matrix(mx_handle_t h) {
     drop_plan(h);
-    cudaFree(h->row_ptr);
-    cudaFree(h->col_ind);
-    cudaFree(h->val);
-    cudaFree(h->x_stage);
-    cudaFree(h->y_stage);
+    void *bufs[] = {h->row_ptr, h->col_ind, h->val, h->x_stage, h->y_stage};
+    for (void *b : bufs)
+        if (b) cudaFreeAsync(b, h->stream);
     h->row_ptr = h->col_ind = nullptr;
     h->val = h->x_stage = h->y_stage = nullptr;
     h->has_matrix = false;
@@ -145,6 +142,15 @@ int mx_create(mx_handle_t *out, int device, int dtype) {
         cudaGetLastError();
         return MX_ERR_INVALID;
     }
+    {
+        // keep freed buffers in the stream-ordered pool: re-extracting a matrix then costs no driver allocation
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+            unsigned long long keep = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+        cudaGetLastError();
+    }
     mx_handle_t h = new mx_handle_s;
     h->device = device;
     h->dtype = dtype;
@@ -162,6 +168,7 @@ int mx_destroy(mx_handle_t h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
     drop_matrix(h);
+    cudaStreamSynchronize(h->stream);
     cudaFree(h->dev_err);
     cudaStreamDestroy(h->stream);
     delete h;
@@ -187,11 +194,11 @@ int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row
     HCK(cudaSetDevice(h->device));
     drop_matrix(h);
     const size_t vb = val_bytes(h->dtype);
-    HCK(cudaMalloc(&h->row_ptr, sizeof(int) * ((size_t)n_rows + 1)));
-    HCK(cudaMalloc(&h->col_ind, sizeof(int) * (size_t)(nnz > 0 ? nnz : 1)));
-    HCK(cudaMalloc(&h->val, vb * (size_t)(nnz > 0 ? nnz : 1)));
-    HCK(cudaMalloc(&h->x_stage, vb * (size_t)(n_cols > 0 ? n_cols : 1)));
-    HCK(cudaMalloc(&h->y_stage, vb * (size_t)(n_rows > 0 ? n_rows : 1)));
+    HCK(cudaMallocAsync(&h->row_ptr, sizeof(int) * ((size_t)n_rows + 1), h->stream));
+    HCK(cudaMallocAsync(&h->col_ind, sizeof(int) * (size_t)(nnz > 0 ? nnz : 1), h->stream));
+    HCK(cudaMallocAsync(&h->val, vb * (size_t)(nnz > 0 ? nnz : 1), h->stream));
+    HCK(cudaMallocAsync(&h->x_stage, vb * (size_t)(n_cols > 0 ? n_cols : 1), h->stream));
+    HCK(cudaMallocAsync(&h->y_stage, vb * (size_t)(n_rows > 0 ? n_rows : 1), h->stream));
     HCK(cudaMemcpyAsync(h->row_ptr, row_ptr, sizeof(int) * ((size_t)n_rows + 1), cudaMemcpyHostToDevice, h->stream));
     if (nnz > 0) {
         HCK(cudaMemcpyAsync(h->col_ind, col_ind, sizeof(int) * (size_t)nnz, cudaMemcpyHostToDevice, h->stream));
@@ -347,14 +354,14 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         HCK(resid_plan_build(h->dtype, h->ddcsr, h->stream));
         h->dd_use_tile = h->dd_mode == MX_DD_TILE ||
                          (h->dd_mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
-        HCK(cudaMalloc(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows));
+        HCK(cudaMallocAsync(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
         HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
-        HCK(cudaMalloc(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols));
+        HCK(cudaMallocAsync(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
         // the same entries numbered by their original columns
         const size_t nAToX = (size_t)h->stats.totalFrags * h->stats.fragK;
-        HCK(cudaMalloc(&h->colInd_CD_orig, sizeof(int) * (size_t)(h->stats.nnzCD > 0 ? h->stats.nnzCD : 1)));
-        HCK(cudaMalloc(&h->colInd_dd_orig, sizeof(int) * (size_t)(h->stats.nnzRowD > 0 ? h->stats.nnzRowD : 1)));
-        HCK(cudaMalloc(&h->AToX_orig, sizeof(int) * (nAToX > 0 ? nAToX : 1)));
+        HCK(cudaMallocAsync(&h->colInd_CD_orig, sizeof(int) * (size_t)(h->stats.nnzCD > 0 ? h->stats.nnzCD : 1), h->stream));
+        HCK(cudaMallocAsync(&h->colInd_dd_orig, sizeof(int) * (size_t)(h->stats.nnzRowD > 0 ? h->stats.nnzRowD : 1), h->stream));
+        HCK(cudaMallocAsync(&h->AToX_orig, sizeof(int) * (nAToX > 0 ? nAToX : 1), h->stream));
         HCK(map_indices(h->part.colInd_CD, h->part.xperm, h->colInd_CD_orig, h->stats.nnzCD, h->stream));
         HCK(map_indices(h->part.colInd_dd, h->part.xperm, h->colInd_dd_orig, h->stats.nnzRowD, h->stream));
         HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
@@ -588,7 +595,7 @@ int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *cs
         if (ce == cudaSuccess) ce = resid_spmv(dtype, P, d_x, d_y, nullptr, nullptr, true, nullptr, 0);  // y += A x
         if (ce == cudaSuccess) ce = cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost);
     }
-    resid_plan_free(P);
+    resid_plan_free(P, 0);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     SCK(ce);
@@ -616,7 +623,7 @@ static int run_tiles(int dtype, TileArrays &T, const void *d_x, void *d_y, void 
     }
     if (ce == cudaSuccess) ce = tile_spmv(dtype, P, d_x, d_y, nullptr, false, accumulate, nullptr, 0);
     if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
-    tile_plan_free(P);
+    tile_plan_free(P, 0);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     SCK(ce);
@@ -688,7 +695,7 @@ int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int 
     } else {
         st = ce != cudaSuccess ? MX_ERR_CUDA : tstatus;
     }
-    tile_arrays_free(T);
+    tile_arrays_free(T, 0);
     for (int i = 0; i < rowA; ++i) order_rid[i] = i;
     return st;
 }

@@ -103,7 +103,7 @@ struct PartArrays {
 
 // ---- launchers (each returns the cudaError_t of its launches) ----
 cudaError_t resid_plan_build(int dtype, ResidPlan &plan, cudaStream_t s);
-void resid_plan_free(ResidPlan &plan);
+void resid_plan_free(ResidPlan &plan, cudaStream_t s);
 // y[r] = sum_r (+ y_in[r] when accumulate) (+ ytile[r] for rows flagged in hotmask).  ytile is of the
 // accumulate type (float for FP16, double for FP64); hotmask has one bit per row.
 cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y, const void *ytile,
@@ -117,7 +117,7 @@ cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, vo
 int resid_launches(const ResidPlan &plan);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
-void tile_plan_free(TilePlan &plan);
+void tile_plan_free(TilePlan &plan, cudaStream_t s);
 // out[row_map ? row_map[i] : i] (accumulate type when out_is_acc, else value type) = tile row i result.
 cudaError_t tile_spmv(int dtype, const TilePlan &plan, const void *x_d, void *out, const int *row_map,
                       bool out_is_acc, bool accumulate, int *dev_err, cudaStream_t s);
@@ -127,8 +127,9 @@ cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, 
                           int *status, cudaStream_t s);
 cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,
                           const void *val_dd, TileArrays &T, int *status, cudaStream_t s);
-void part_arrays_free(PartArrays &P);
-void tile_arrays_free(TileArrays &T);
+// every buffer of the library comes from the stream-ordered pool: allocate and free on the stream that uses it
+void part_arrays_free(PartArrays &P, cudaStream_t s);
+void tile_arrays_free(TileArrays &T, cudaStream_t s);
 
 // out[i] = map[in[i]]
 cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s);

@@ -32,8 +32,8 @@ namespace {
     } while (0)
 
 template <typename T>
-cudaError_t dalloc(T **p, size_t n) {
-    return cudaMalloc((void **)p, (n > 0 ? n : 1) * sizeof(T));
+cudaError_t dalloc(T **p, size_t n, cudaStream_t s) {
+    return cudaMallocAsync((void **)p, (n > 0 ? n : 1) * sizeof(T), s);
 }
 // scratch buffers of one run, taken from the stream-ordered pool (no device-wide synchronisation per buffer) and
 // released on every exit path
@@ -244,7 +244,7 @@ cudaError_t seg_sort_pairs(TempBuf &tmp, const int *kin, int *kout, const int *v
     if (n <= 0 || nseg <= 0) return cudaSuccess;
     size_t bytes = 0;
     PCK(cub::DeviceSegmentedSort::SortPairs(nullptr, bytes, kin, kout, vin, vout, n, nseg, offsets, offsets + 1, s));
-    PCK(tmp.reserve(bytes));
+    PCK(tmp.reserve(bytes, s));
     return cub::DeviceSegmentedSort::SortPairs(tmp.p, bytes, kin, kout, vin, vout, n, nseg, offsets, offsets + 1, s);
 }
 
@@ -253,7 +253,7 @@ cudaError_t sort_desc_pairs(TempBuf &tmp, const int *kin, int *kout, const int *
     if (n <= 0) return cudaSuccess;
     size_t bytes = 0;
     PCK(cub::DeviceRadixSort::SortPairsDescending(nullptr, bytes, kin, kout, vin, vout, n, 0, 32, s));
-    PCK(tmp.reserve(bytes));
+    PCK(tmp.reserve(bytes, s));
     return cub::DeviceRadixSort::SortPairsDescending(tmp.p, bytes, kin, kout, vin, vout, n, 0, 32, s);
 }
 
@@ -280,7 +280,7 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
     PCK(sc.alloc(&head, (size_t)nnzRowD));
     PCK(sc.alloc(&H, (size_t)nnzRowD));
     PCK(sc.alloc(&nf, (size_t)chunkNum + 1));
-    PCK(dalloc(&T.chunkPtr, (size_t)chunkNum + 1));
+    PCK(dalloc(&T.chunkPtr, (size_t)chunkNum + 1, s));
     k_panel_off<<<nblk(chunkNum + 1), 256, 0, s>>>(rowPtr_dd, dRows, chunkNum, panelOff);
     if (nnzRowD > 0) {
         k_expand_rows<<<nblk((long long)dRows * 32), 256, 0, s>>>(rowPtr_dd, dRows, rowOf);
@@ -299,10 +299,10 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
         *status = MX_ERR_OVERFLOW;
         totalFrags = 0;
     }
-    PCK(dalloc(&T.AToX, (size_t)totalFrags * K + 8));  // +slack: bulk copies round up to 16 bytes
-    PCK(dalloc((B **)&T.fragBit, (size_t)totalFrags + 8));
-    PCK(dalloc(&T.fragPtr, (size_t)totalFrags + 1 + 8));
-    PCK(dalloc((V **)&T.tcVal, (size_t)nnzRowD + 16));
+    PCK(dalloc(&T.AToX, (size_t)totalFrags * K + 8, s));  // +slack: bulk copies round up to 16 bytes
+    PCK(dalloc((B **)&T.fragBit, (size_t)totalFrags + 8, s));
+    PCK(dalloc(&T.fragPtr, (size_t)totalFrags + 1 + 8, s));
+    PCK(dalloc((V **)&T.tcVal, (size_t)nnzRowD + 16, s));
     PCK(sc.alloc(&pc, (size_t)totalFrags + 1));
     PCK(sc.alloc(&entFrag, (size_t)nnzRowD));
     PCK(sc.alloc(&entBit, (size_t)nnzRowD));
@@ -365,7 +365,7 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     PCK(sc.alloc(&isS, (size_t)C));
     PCK(sc.alloc(&sidx, (size_t)C));
     PCK(sc.alloc(&colMap, (size_t)C));
-    PCK(dalloc(&P.xperm, (size_t)C));
+    PCK(dalloc(&P.xperm, (size_t)C, s));
     k_fill<<<nblk(C), 256, 0, s>>>(isS, C, 1);
     k_mark_rank<<<nblk(dCols), 256, 0, s>>>(colOrder, dCols, rankOf, isS);
     PCK(exclusive_sum(tmp, isS, sidx, C, s));
@@ -389,14 +389,14 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     }
     const int sRows = R - dRows, nnzRowS = nnzColD - nnzRowD, nnzCD = nnzColS + nnzRowS;
     PCK(sc.alloc(&hotPos, (size_t)R));
-    PCK(dalloc(&P.rId, (size_t)dRows));
-    PCK(dalloc(&P.hotmask, (size_t)(R + 31) / 32));
+    PCK(dalloc(&P.rId, (size_t)dRows, s));
+    PCK(dalloc(&P.hotmask, (size_t)(R + 31) / 32, s));
     PCK(cudaMemsetAsync(P.hotmask, 0, ((size_t)(R + 31) / 32) * sizeof(uint32_t), s));
     k_fill<<<nblk(R), 256, 0, s>>>(hotPos, R, -1);
     k_mark_hot<<<nblk(dRows), 256, 0, s>>>(rowOrder, dRows, hotPos, P.hotmask, P.rId);
     // 7: row pointers of dd (lengths = the first dRows sorted counts) and of the residual
-    PCK(dalloc(&P.rowPtr_dd, (size_t)dRows + 1));
-    PCK(dalloc(&P.rowPtr_CD, (size_t)R + 1));
+    PCK(dalloc(&P.rowPtr_dd, (size_t)dRows + 1, s));
+    PCK(dalloc(&P.rowPtr_CD, (size_t)R + 1, s));
     PCK(sc.alloc(&resLen, (size_t)R + 1));
     PCK(exclusive_sum(tmp, sortedRCnt, P.rowPtr_dd, dRows, s));
     PCK(cudaMemcpyAsync(P.rowPtr_dd + dRows, &nnzRowD, sizeof(int), cudaMemcpyHostToDevice, s));
@@ -410,10 +410,10 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     PCK(sc.alloc(&Pdd2, (size_t)nnzRowD));
     PCK(sc.alloc(&Kcd2, (size_t)nnzCD));
     PCK(sc.alloc(&Pcd2, (size_t)nnzCD));
-    PCK(dalloc(&P.colInd_dd, (size_t)nnzRowD));
-    PCK(dalloc(&P.colInd_CD, (size_t)nnzCD));
-    PCK(dalloc((V **)&P.val_dd, (size_t)nnzRowD));
-    PCK(dalloc((V **)&P.val_CD, (size_t)nnzCD));
+    PCK(dalloc(&P.colInd_dd, (size_t)nnzRowD, s));
+    PCK(dalloc(&P.colInd_CD, (size_t)nnzCD, s));
+    PCK(dalloc((V **)&P.val_dd, (size_t)nnzRowD, s));
+    PCK(dalloc((V **)&P.val_CD, (size_t)nnzCD, s));
     k_scatter<<<nblk((long long)R * 32), 256, 0, s>>>(A.row_ptr, A.col_ind, colMap, hotPos, P.rowPtr_dd, P.rowPtr_CD,
                                                       dCols, sCols, R, Kdd, Pdd, Kcd, Pcd);
     PCK(seg_sort_pairs(tmp, Kdd, P.colInd_dd, Pdd, Pdd2, nnzRowD, dRows, P.rowPtr_dd, s));
@@ -464,26 +464,18 @@ cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_d
                                              s);
 }
 
-void part_arrays_free(PartArrays &P) {
-    cudaFree(P.xperm);
-    cudaFree(P.rId);
-    cudaFree(P.hotmask);
-    cudaFree(P.rowPtr_dd);
-    cudaFree(P.colInd_dd);
-    cudaFree(P.val_dd);
-    cudaFree(P.rowPtr_CD);
-    cudaFree(P.colInd_CD);
-    cudaFree(P.val_CD);
-    tile_arrays_free(P.tiles);
+void part_arrays_free(PartArrays &P, cudaStream_t s) {
+    void *bufs[] = {P.xperm, P.rId, P.hotmask, P.rowPtr_dd, P.colInd_dd, P.val_dd, P.rowPtr_CD, P.colInd_CD, P.val_CD};
+    for (void *b : bufs)
+        if (b) cudaFreeAsync(b, s);
+    tile_arrays_free(P.tiles, s);
     P = PartArrays();
 }
 
-void tile_arrays_free(TileArrays &T) {
-    cudaFree(T.chunkPtr);
-    cudaFree(T.AToX);
-    cudaFree(T.fragPtr);
-    cudaFree(T.fragBit);
-    cudaFree(T.tcVal);
+void tile_arrays_free(TileArrays &T, cudaStream_t s) {
+    void *bufs[] = {T.chunkPtr, T.AToX, T.fragPtr, T.fragBit, T.tcVal};
+    for (void *b : bufs)
+        if (b) cudaFreeAsync(b, s);
     T = TileArrays();
 }
 

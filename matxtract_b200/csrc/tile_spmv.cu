@@ -373,10 +373,10 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     }
     int *segCount = nullptr, *multiCount = nullptr, *firstSlot = nullptr;
     size_t np = (size_t)P.A.chunkNum + 1;
-    if ((e = cudaMalloc(&segCount, np * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&multiCount, np * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&firstSlot, np * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.panelFirstSeg, np * sizeof(int))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&segCount, np * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&multiCount, np * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&firstSlot, np * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.panelFirstSeg, np * sizeof(int), s)) != cudaSuccess) return e;
     seg_count_kernel<<<(int)((np + 255) / 256), 256, 0, s>>>(P.A.chunkPtr, P.A.chunkNum, segCount, multiCount);
     TempBuf tmp;
     if ((e = exclusive_sum(tmp, segCount, P.panelFirstSeg, (int)np, s)) != cudaSuccess) return e;
@@ -392,33 +392,33 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     P.numSegs = totals[0];
     P.numMultiSegs = totals[1];
     size_t ns = (size_t)P.numSegs;
-    if ((e = cudaMalloc(&P.segPanel, ns * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.segBegin, ns * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.segEnd, ns * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.segSlot, ns * sizeof(int))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&P.partial, (size_t)(P.numMultiSegs > 0 ? P.numMultiSegs : 1) * 8 * acc_bytes(dtype))) !=
-        cudaSuccess)
+    if ((e = cudaMallocAsync(&P.segPanel, ns * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.segBegin, ns * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.segEnd, ns * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.segSlot, ns * sizeof(int), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.partial, (size_t)(P.numMultiSegs > 0 ? P.numMultiSegs : 1) * 8 * acc_bytes(dtype),
+                             s)) != cudaSuccess)
         return e;
-    if ((e = cudaMalloc(&P.panelCount, (size_t)P.A.chunkNum * sizeof(unsigned))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.panelCount, (size_t)P.A.chunkNum * sizeof(unsigned), s)) != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(P.panelCount, 0, (size_t)P.A.chunkNum * sizeof(unsigned), s)) != cudaSuccess) return e;
     seg_fill_kernel<<<(P.A.chunkNum + 255) / 256, 256, 0, s>>>(P.A.chunkPtr, P.A.chunkNum, P.panelFirstSeg, firstSlot,
                                                              P.segPanel, P.segBegin, P.segEnd, P.segSlot);
     e = cudaGetLastError();
     cudaError_t e2 = cudaStreamSynchronize(s);
-    cudaFree(segCount);
-    cudaFree(multiCount);
-    cudaFree(firstSlot);
+    if (segCount) cudaFreeAsync(segCount, s);
+    if (multiCount) cudaFreeAsync(multiCount, s);
+    if (firstSlot) cudaFreeAsync(firstSlot, s);
     if (e != cudaSuccess) return e;
     if (e2 != cudaSuccess) return e2;
-    if ((e = cudaMalloc(&P.segDesc, (ns > 0 ? ns : 1) * sizeof(int4))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.segDesc, (ns > 0 ? ns : 1) * sizeof(int4), s)) != cudaSuccess) return e;
     seg_pack_kernel<<<(P.numSegs + 255) / 256, 256, 0, s>>>(P.segPanel, P.segBegin, P.segEnd, P.segSlot, P.numSegs,
                                                             (int4 *)P.segDesc);
     // CTA descriptors of the TMA-staged kernel: consecutive segments grouped by the bytes they stage
     long long *cost = nullptr, *prefix = nullptr;
     unsigned *maxBytes = nullptr;
-    if ((e = cudaMalloc(&cost, (ns + 1) * sizeof(long long))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&prefix, (ns + 1) * sizeof(long long))) != cudaSuccess) return e;
-    if ((e = cudaMalloc(&maxBytes, sizeof(unsigned))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&cost, (ns + 1) * sizeof(long long), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&prefix, (ns + 1) * sizeof(long long), s)) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&maxBytes, sizeof(unsigned), s)) != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(maxBytes, 0, sizeof(unsigned), s)) != cudaSuccess) return e;
     const int cgrid = (P.numSegs + 1 + 255) / 256;
     if (dtype == MX_FP64)
@@ -436,7 +436,7 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     const int STAGE_BYTES = g_stage_bytes;
     P.numCtas = (int)((totalBytes + STAGE_BYTES - 1) / STAGE_BYTES);
     if (P.numCtas < 1) P.numCtas = 1;
-    if ((e = cudaMalloc(&P.ctaDesc, (size_t)P.numCtas * sizeof(CtaDesc))) != cudaSuccess) return e;
+    if ((e = cudaMallocAsync(&P.ctaDesc, (size_t)P.numCtas * sizeof(CtaDesc), s)) != cudaSuccess) return e;
     if (dtype == MX_FP64)
         cta_desc_kernel<uint32_t, double, 4><<<(P.numCtas + 127) / 128, 128, 0, s>>>(
             prefix, P.segBegin, P.segEnd, P.A.fragPtr, P.numSegs, P.numCtas, STAGE_BYTES, (CtaDesc *)P.ctaDesc, maxBytes);
@@ -447,23 +447,23 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     if ((e = cudaMemcpyAsync(&mb, maxBytes, sizeof(unsigned), cudaMemcpyDeviceToHost, s)) != cudaSuccess) return e;
     e = cudaStreamSynchronize(s);
     P.stageBytes = (int)mb;
-    cudaFree(cost);
-    cudaFree(prefix);
-    cudaFree(maxBytes);
+    if (cost) cudaFreeAsync(cost, s);
+    if (prefix) cudaFreeAsync(prefix, s);
+    if (maxBytes) cudaFreeAsync(maxBytes, s);
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
 
-void tile_plan_free(TilePlan &P) {
-    cudaFree(P.segPanel);
-    cudaFree(P.segBegin);
-    cudaFree(P.segEnd);
-    cudaFree(P.segSlot);
-    cudaFree(P.panelFirstSeg);
-    cudaFree(P.partial);
-    cudaFree(P.panelCount);
-    cudaFree(P.ctaDesc);
-    cudaFree(P.segDesc);
+void tile_plan_free(TilePlan &P, cudaStream_t s) {
+    if (P.segPanel) cudaFreeAsync(P.segPanel, s);
+    if (P.segBegin) cudaFreeAsync(P.segBegin, s);
+    if (P.segEnd) cudaFreeAsync(P.segEnd, s);
+    if (P.segSlot) cudaFreeAsync(P.segSlot, s);
+    if (P.panelFirstSeg) cudaFreeAsync(P.panelFirstSeg, s);
+    if (P.partial) cudaFreeAsync(P.partial, s);
+    if (P.panelCount) cudaFreeAsync(P.panelCount, s);
+    if (P.ctaDesc) cudaFreeAsync(P.ctaDesc, s);
+    if (P.segDesc) cudaFreeAsync(P.segDesc, s);
     P.ctaDesc = P.segDesc = nullptr;
     P.numCtas = 0;
     P.segPanel = P.segBegin = P.segEnd = P.segSlot = P.panelFirstSeg = nullptr;
