@@ -72,6 +72,22 @@ typedef struct {
  * row-partitioned matrix) is accepted as well and is extracted on its own. */
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats);
 int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats);
+/* Shape of the matrix the handle holds (uploaded, or restored by mx_load_partition). */
+int mx_dims(mx_handle_t h, int *n_rows, int *n_cols, int *nnz);
+
+/* Stores / restores a partition so that the extraction is paid once per matrix (successor of the reference's
+ * `<matrix>_preprocessed[_fp16].dat` dump, test/tcpreprocess.cpp:1208-1255, which held the fragment format only).
+ * The file holds every array of mx_partition_arrays plus the counts; it is enough to multiply: mx_load_partition
+ * needs no uploaded matrix (and drops one that is there), builds the execution plans and leaves the handle ready for
+ * mx_spmv.  A loaded handle cannot be re-extracted with other taus (the original CSR is not in the file). */
+int mx_save_partition(mx_handle_t h, const char *path);
+int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats);
+
+/* Searches (tau_c, tau_r) on the device instead of the reference's 20-run Bayesian search through the command-line
+ * driver (ML/bayes_opt.py:153-163): every valid point of the grid {0, 1/grid, ..., (grid-1)/grid}^2 with
+ * tau_c >= tau_r is extracted and its product timed (3 warm + 10 timed); the fastest is left installed in the handle.
+ * ms_plain is the time of tau = (0,0). */
+int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float *ms_best, float *ms_plain);
 
 /* Host destinations for the arrays of the partition, in the reference's layout; a NULL member is skipped.
  * Sizes follow from mx_partition_stats (K = fragK). */

@@ -60,6 +60,10 @@ SYMBOLS = {
     "mx_upload_csr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "mx_partition": (_i, [_vp, _d, _d, C.POINTER(PartitionStats)]),
     "mx_partition_stats_get": (_i, [_vp, C.POINTER(PartitionStats)]),
+    "mx_save_partition": (_i, [_vp, C.c_char_p]),
+    "mx_load_partition": (_i, [_vp, C.c_char_p, C.POINTER(PartitionStats)]),
+    "mx_autotune_tau": (_i, [_vp, _i, C.POINTER(_d), C.POINTER(_d), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mx_dims": (_i, [_vp, _ip, _ip, _ip]),
     "mx_download_partition": (_i, [_vp, C.POINTER(_PartitionArrays)]),
     "mx_spmv": (_i, [_vp, _vp, _vp]),
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
@@ -160,6 +164,29 @@ class MatXtract:
         self._ck(lib().mx_partition(self._h, float(tau_c), float(tau_r), C.byref(st)))
         self.stats = st
         return st
+
+    def save_partition(self, path):
+        self._ck(lib().mx_save_partition(self._h, str(path).encode()))
+
+    def load_partition(self, path) -> PartitionStats:
+        """Restores a stored partition; the handle is then ready for spmv without an uploaded matrix."""
+        st = PartitionStats()
+        self._ck(lib().mx_load_partition(self._h, str(path).encode(), C.byref(st)))
+        self.stats = st
+        r, c, z = C.c_int(), C.c_int(), C.c_int()
+        self._ck(lib().mx_dims(self._h, C.byref(r), C.byref(c), C.byref(z)))
+        self.n_rows, self.n_cols, self.nnz = r.value, c.value, z.value
+        return st
+
+    def autotune_tau(self, grid: int = 4):
+        """Times every valid (tau_c, tau_r) of a grid on the device and installs the fastest.
+        Returns (tau_c, tau_r, ms of the best, ms of tau = (0,0))."""
+        tc, tr, mb, mp = C.c_double(), C.c_double(), C.c_float(), C.c_float()
+        self._ck(lib().mx_autotune_tau(self._h, grid, C.byref(tc), C.byref(tr), C.byref(mb), C.byref(mp)))
+        st = PartitionStats()
+        self._ck(lib().mx_partition_stats_get(self._h, C.byref(st)))
+        self.stats = st
+        return tc.value, tr.value, mb.value, mp.value
 
     def download_partition(self) -> dict:
         s = self.stats

@@ -288,6 +288,47 @@ static int tune_colspace(mx_handle_t h) {
     return MX_OK;
 }
 
+// Everything that follows the extraction proper (or the loading of a stored partition): execution plans of the two
+// halves, the carrier, the index arrays in original column numbering, and the choice of the execution column space.
+static int finish_partition(mx_handle_t h) {
+    h->resid.n_rows = h->n_rows;
+    h->resid.n_cols = h->n_cols;
+    h->resid.nnz = h->stats.nnzCD;
+    h->resid.row_ptr = h->part.rowPtr_CD;
+    h->resid.col_ind = h->part.colInd_CD;
+    h->resid.val = h->part.val_CD;
+    HCK(resid_plan_build(h->dtype, h->resid, h->stream));
+    h->tile.A = h->part.tiles;
+    HCK(tile_plan_build(h->dtype, h->tile, h->stream));
+    h->ddcsr.n_rows = h->stats.dRows;
+    h->ddcsr.n_cols = h->stats.dCols;
+    h->ddcsr.nnz = h->stats.nnzRowD;
+    h->ddcsr.row_ptr = h->part.rowPtr_dd;
+    h->ddcsr.col_ind = h->part.colInd_dd;
+    h->ddcsr.val = h->part.val_dd;
+    HCK(resid_plan_build(h->dtype, h->ddcsr, h->stream));
+    h->dd_use_tile = h->dd_mode == MX_DD_TILE ||
+                     (h->dd_mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
+    HCK(cudaMallocAsync(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
+    HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
+    HCK(cudaMallocAsync(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
+    // the same entries numbered by their original columns
+    const size_t nAToX = (size_t)h->stats.totalFrags * h->stats.fragK;
+    HCK(cudaMallocAsync(&h->colInd_CD_orig, sizeof(int) * (size_t)(h->stats.nnzCD > 0 ? h->stats.nnzCD : 1), h->stream));
+    HCK(cudaMallocAsync(&h->colInd_dd_orig, sizeof(int) * (size_t)(h->stats.nnzRowD > 0 ? h->stats.nnzRowD : 1), h->stream));
+    HCK(cudaMallocAsync(&h->AToX_orig, sizeof(int) * (nAToX > 0 ? nAToX : 1), h->stream));
+    HCK(map_indices(h->part.colInd_CD, h->part.xperm, h->colInd_CD_orig, h->stats.nnzCD, h->stream));
+    HCK(map_indices(h->part.colInd_dd, h->part.xperm, h->colInd_dd_orig, h->stats.nnzRowD, h->stream));
+    HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
+    h->planned = true;  // the tuner runs real products
+    int tst = tune_colspace(h);
+    if (tst != MX_OK) {
+        drop_plan(h);
+        return tst;
+    }
+    return MX_OK;
+}
+
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats) {
     if (!h) return MX_ERR_INVALID;
     if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_partition: no matrix uploaded");
@@ -336,41 +377,8 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
             return h->fail(status, status == MX_ERR_TAU ? "tau threshold never reached by the ranking prefix"
                                                         : "fragment count exceeds int32");
         }
-        h->resid.n_rows = h->n_rows;
-        h->resid.n_cols = h->n_cols;
-        h->resid.nnz = h->stats.nnzCD;
-        h->resid.row_ptr = h->part.rowPtr_CD;
-        h->resid.col_ind = h->part.colInd_CD;
-        h->resid.val = h->part.val_CD;
-        HCK(resid_plan_build(h->dtype, h->resid, h->stream));
-        h->tile.A = h->part.tiles;
-        HCK(tile_plan_build(h->dtype, h->tile, h->stream));
-        h->ddcsr.n_rows = h->stats.dRows;
-        h->ddcsr.n_cols = h->stats.dCols;
-        h->ddcsr.nnz = h->stats.nnzRowD;
-        h->ddcsr.row_ptr = h->part.rowPtr_dd;
-        h->ddcsr.col_ind = h->part.colInd_dd;
-        h->ddcsr.val = h->part.val_dd;
-        HCK(resid_plan_build(h->dtype, h->ddcsr, h->stream));
-        h->dd_use_tile = h->dd_mode == MX_DD_TILE ||
-                         (h->dd_mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
-        HCK(cudaMallocAsync(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
-        HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
-        HCK(cudaMallocAsync(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
-        // the same entries numbered by their original columns
-        const size_t nAToX = (size_t)h->stats.totalFrags * h->stats.fragK;
-        HCK(cudaMallocAsync(&h->colInd_CD_orig, sizeof(int) * (size_t)(h->stats.nnzCD > 0 ? h->stats.nnzCD : 1), h->stream));
-        HCK(cudaMallocAsync(&h->colInd_dd_orig, sizeof(int) * (size_t)(h->stats.nnzRowD > 0 ? h->stats.nnzRowD : 1), h->stream));
-        HCK(cudaMallocAsync(&h->AToX_orig, sizeof(int) * (nAToX > 0 ? nAToX : 1), h->stream));
-        HCK(map_indices(h->part.colInd_CD, h->part.xperm, h->colInd_CD_orig, h->stats.nnzCD, h->stream));
-        HCK(map_indices(h->part.colInd_dd, h->part.xperm, h->colInd_dd_orig, h->stats.nnzRowD, h->stream));
-        HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
-        h->planned = true;  // the tuner runs real products
-        int tst = tune_colspace(h);
-        if (tst != MX_OK) {
-            drop_plan(h);
-            return tst;
-        }
+        int fst = finish_partition(h);
+        if (fst != MX_OK) return fst;
     }
     HCK(cudaEventRecord(e1, h->stream));
     HCK(cudaEventSynchronize(e1));
@@ -381,6 +389,197 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
     h->stats.preprocess_ms = ms;
     h->planned = true;
     if (stats) *stats = h->stats;
+    return MX_OK;
+}
+
+// ---- stored partitions ---------------------------------------------------------------------------------------
+namespace {
+const char kMagic[8] = {'M', 'X', 'P', 'A', 'R', 'T', '0', '1'};
+struct FileHeader {
+    char magic[8];
+    int32_t dtype, n_rows, n_cols, nnz;
+    int32_t dCols, nnzColD, sCols, nnzColS, dRows, nnzRowD, sRows, nnzRowS, chunkNum, totalFrags, nnzCD, fragK;
+    double tc_nnz_ratio;
+};
+struct FileCloser {
+    FILE *f;
+    ~FileCloser() {
+        if (f) fclose(f);
+    }
+};
+}  // namespace
+
+int mx_save_partition(mx_handle_t h, const char *path) {
+    if (!h || !path) return MX_ERR_INVALID;
+    if (!h->planned || !h->stats.active) return h->fail(MX_ERR_STATE, "mx_save_partition: no active partition");
+    HCK(cudaSetDevice(h->device));
+    const mx_partition_stats &s = h->stats;
+    const size_t vb = val_bytes(h->dtype), bb = bit_bytes(h->dtype);
+    FileHeader hd{};
+    memcpy(hd.magic, kMagic, 8);
+    hd.dtype = h->dtype;
+    hd.n_rows = h->n_rows;
+    hd.n_cols = h->n_cols;
+    hd.nnz = h->nnz;
+    hd.dCols = s.dCols, hd.nnzColD = s.nnzColD, hd.sCols = s.sCols, hd.nnzColS = s.nnzColS;
+    hd.dRows = s.dRows, hd.nnzRowD = s.nnzRowD, hd.sRows = s.sRows, hd.nnzRowS = s.nnzRowS;
+    hd.chunkNum = s.chunkNum, hd.totalFrags = s.totalFrags, hd.nnzCD = s.nnzCD, hd.fragK = s.fragK;
+    hd.tc_nnz_ratio = s.tc_nnz_ratio;
+    FileCloser fc{fopen(path, "wb")};
+    if (!fc.f) return h->fail(MX_ERR_INVALID, std::string("cannot open for writing: ") + path);
+    if (fwrite(&hd, sizeof hd, 1, fc.f) != 1) return h->fail(MX_ERR_INVALID, "write failed");
+    struct Arr {
+        const void *dev;
+        size_t bytes;
+    } arrs[] = {{h->part.xperm, sizeof(int) * (size_t)h->n_cols},
+                {h->part.rId, sizeof(int) * (size_t)s.dRows},
+                {h->part.rowPtr_dd, sizeof(int) * ((size_t)s.dRows + 1)},
+                {h->part.colInd_dd, sizeof(int) * (size_t)s.nnzRowD},
+                {h->part.val_dd, vb * (size_t)s.nnzRowD},
+                {h->part.tiles.chunkPtr, sizeof(int) * ((size_t)s.chunkNum + 1)},
+                {h->part.tiles.AToX, sizeof(int) * (size_t)s.totalFrags * s.fragK},
+                {h->part.tiles.fragPtr, sizeof(int) * ((size_t)s.totalFrags + 1)},
+                {h->part.tiles.fragBit, bb * (size_t)s.totalFrags},
+                {h->part.tiles.tcVal, vb * (size_t)s.nnzRowD},
+                {h->part.rowPtr_CD, sizeof(int) * ((size_t)h->n_rows + 1)},
+                {h->part.colInd_CD, sizeof(int) * (size_t)s.nnzCD},
+                {h->part.val_CD, vb * (size_t)s.nnzCD}};
+    std::string buf;
+    for (const Arr &a : arrs) {
+        const uint64_t n = a.bytes;
+        if (fwrite(&n, sizeof n, 1, fc.f) != 1) return h->fail(MX_ERR_INVALID, "write failed");
+        if (n == 0) continue;
+        buf.resize(n);
+        HCK(cudaMemcpyAsync(&buf[0], a.dev, n, cudaMemcpyDeviceToHost, h->stream));
+        HCK(cudaStreamSynchronize(h->stream));
+        if (fwrite(buf.data(), 1, n, fc.f) != n) return h->fail(MX_ERR_INVALID, "write failed");
+    }
+    return MX_OK;
+}
+
+int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats) {
+    if (!h || !path) return MX_ERR_INVALID;
+    FileCloser fc{fopen(path, "rb")};
+    if (!fc.f) return h->fail(MX_ERR_INVALID, std::string("cannot open: ") + path);
+    FileHeader hd{};
+    if (fread(&hd, sizeof hd, 1, fc.f) != 1 || memcmp(hd.magic, kMagic, 8) != 0)
+        return h->fail(MX_ERR_INVALID, "not a stored partition");
+    if (hd.dtype != h->dtype) return h->fail(MX_ERR_INVALID, "stored partition has the other value type");
+    if (hd.n_rows < 0 || hd.n_cols < 0 || hd.dRows < 0 || hd.nnzRowD < 0 || hd.nnzCD < 0 || hd.totalFrags < 0 ||
+        hd.fragK != frag_k(h->dtype))
+        return h->fail(MX_ERR_INVALID, "stored partition: bad header");
+    HCK(cudaSetDevice(h->device));
+    drop_matrix(h);  // a loaded partition replaces the matrix: it holds every entry (no re-extraction from it)
+    h->n_rows = hd.n_rows;
+    h->n_cols = hd.n_cols;
+    h->nnz = hd.nnz;
+    mx_partition_stats &s = h->stats;
+    s = mx_partition_stats{};
+    s.dCols = hd.dCols, s.nnzColD = hd.nnzColD, s.sCols = hd.sCols, s.nnzColS = hd.nnzColS;
+    s.dRows = hd.dRows, s.nnzRowD = hd.nnzRowD, s.sRows = hd.sRows, s.nnzRowS = hd.nnzRowS;
+    s.chunkNum = hd.chunkNum, s.totalFrags = hd.totalFrags, s.nnzCD = hd.nnzCD, s.fragK = hd.fragK;
+    s.tc_nnz_ratio = hd.tc_nnz_ratio;
+    s.active = 1;
+    const size_t vb = val_bytes(h->dtype), bb = bit_bytes(h->dtype);
+    struct Arr {
+        void **dev;
+        size_t bytes, slack;
+    } arrs[] = {{(void **)&h->part.xperm, sizeof(int) * (size_t)h->n_cols, 0},
+                {(void **)&h->part.rId, sizeof(int) * (size_t)s.dRows, 0},
+                {(void **)&h->part.rowPtr_dd, sizeof(int) * ((size_t)s.dRows + 1), 0},
+                {(void **)&h->part.colInd_dd, sizeof(int) * (size_t)s.nnzRowD, 0},
+                {(void **)&h->part.val_dd, vb * (size_t)s.nnzRowD, 0},
+                {(void **)&h->part.tiles.chunkPtr, sizeof(int) * ((size_t)s.chunkNum + 1), 0},
+                {(void **)&h->part.tiles.AToX, sizeof(int) * (size_t)s.totalFrags * s.fragK, 64},
+                {(void **)&h->part.tiles.fragPtr, sizeof(int) * ((size_t)s.totalFrags + 1), 64},
+                {(void **)&h->part.tiles.fragBit, bb * (size_t)s.totalFrags, 64},
+                {(void **)&h->part.tiles.tcVal, vb * (size_t)s.nnzRowD, 64},
+                {(void **)&h->part.rowPtr_CD, sizeof(int) * ((size_t)h->n_rows + 1), 0},
+                {(void **)&h->part.colInd_CD, sizeof(int) * (size_t)s.nnzCD, 0},
+                {(void **)&h->part.val_CD, vb * (size_t)s.nnzCD, 0}};
+    std::string buf;
+    for (const Arr &a : arrs) {
+        uint64_t n = 0;
+        if (fread(&n, sizeof n, 1, fc.f) != 1 || n != a.bytes) {
+            drop_plan(h);
+            return h->fail(MX_ERR_INVALID, "stored partition: array size does not match its header");
+        }
+        HCK(cudaMallocAsync(a.dev, a.bytes + a.slack + 16, h->stream));  // slack: bulk copies round up to 16 bytes
+        if (n == 0) continue;
+        buf.resize(n);
+        if (fread(&buf[0], 1, n, fc.f) != n) {
+            drop_plan(h);
+            return h->fail(MX_ERR_INVALID, "stored partition: truncated file");
+        }
+        HCK(cudaMemcpyAsync(*a.dev, buf.data(), n, cudaMemcpyHostToDevice, h->stream));
+        HCK(cudaStreamSynchronize(h->stream));
+    }
+    h->part.tiles.dRows = s.dRows;
+    h->part.tiles.dCols = s.dCols;
+    h->part.tiles.chunkNum = s.chunkNum;
+    h->part.tiles.totalFrags = s.totalFrags;
+    h->part.tiles.nvals = s.nnzRowD;
+    HCK(hotmask_from_rid(h->part.rId, s.dRows, h->n_rows, &h->part.hotmask, h->stream));
+    HCK(cudaMallocAsync(&h->x_stage, vb * (size_t)(h->n_cols > 0 ? h->n_cols : 1), h->stream));
+    HCK(cudaMallocAsync(&h->y_stage, vb * (size_t)(h->n_rows > 0 ? h->n_rows : 1), h->stream));
+    int st = finish_partition(h);
+    if (st != MX_OK) return st;
+    HCK(cudaStreamSynchronize(h->stream));
+    if (stats) *stats = h->stats;
+    return MX_OK;
+}
+
+// ---- tau search on the device --------------------------------------------------------------------------------
+int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float *ms_best, float *ms_plain) {
+    if (!h || grid < 1 || grid > 16 || !tau_c || !tau_r) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_autotune_tau: no matrix uploaded");
+    HCK(cudaSetDevice(h->device));
+    cudaEvent_t e0, e1;
+    HCK(cudaEventCreate(&e0));
+    HCK(cudaEventCreate(&e1));
+    double bc = 0, br = 0;
+    float best = -1.f, plain = 0.f;
+    for (int i = 0; i < grid; ++i)
+        for (int j = 0; j <= i; ++j) {
+            if (i == 0 && j > 0) continue;
+            const double tc = (double)i / grid, tr = (double)j / grid;
+            int st = mx_partition(h, tc, tr, nullptr);
+            if (st == MX_ERR_TAU) continue;  // no prefix of the ranking reaches the threshold: not a candidate
+            if (st != MX_OK) return st;
+            HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
+            for (int it = 0; it < 3 + 10; ++it) {
+                if (it == 3) HCK(cudaEventRecord(e0, h->stream));
+                st = spmv_enqueue(h, h->x_stage, h->y_stage, true, true);
+                if (st != MX_OK) return st;
+            }
+            HCK(cudaEventRecord(e1, h->stream));
+            HCK(cudaEventSynchronize(e1));
+            float ms = 0;
+            HCK(cudaEventElapsedTime(&ms, e0, e1));
+            ms /= 10;
+            if (i == 0) plain = ms;
+            if (best < 0 || ms < best) {
+                best = ms;
+                bc = tc;
+                br = tr;
+            }
+        }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    int st = mx_partition(h, bc, br, nullptr);
+    if (st != MX_OK) return st;
+    *tau_c = bc;
+    *tau_r = br;
+    if (ms_best) *ms_best = best;
+    if (ms_plain) *ms_plain = plain;
+    return MX_OK;
+}
+
+int mx_dims(mx_handle_t h, int *n_rows, int *n_cols, int *nnz) {
+    if (!h) return MX_ERR_INVALID;
+    if (n_rows) *n_rows = h->n_rows;
+    if (n_cols) *n_cols = h->n_cols;
+    if (nnz) *nnz = h->nnz;
     return MX_OK;
 }
 

@@ -127,6 +127,8 @@ cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, 
                           int *status, cudaStream_t s);
 cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,
                           const void *val_dd, TileArrays &T, int *status, cudaStream_t s);
+// bit r set for every r in rId (a stored partition carries rId, not the bitmap)
+cudaError_t hotmask_from_rid(const int *rId, int dRows, int n_rows, uint32_t **hotmask, cudaStream_t s);
 // every buffer of the library comes from the stream-ordered pool: allocate and free on the stream that uses it
 void part_arrays_free(PartArrays &P, cudaStream_t s);
 void tile_arrays_free(TileArrays &T, cudaStream_t s);

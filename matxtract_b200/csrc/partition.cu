@@ -464,6 +464,22 @@ cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_d
                                              s);
 }
 
+__global__ void k_hotmask_from_rid(const int *__restrict__ rId, int dRows, uint32_t *__restrict__ hotmask) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dRows) return;
+    int r = rId[i];
+    atomicOr(hotmask + (r >> 5), 1u << (r & 31));
+}
+
+cudaError_t hotmask_from_rid(const int *rId, int dRows, int n_rows, uint32_t **hotmask, cudaStream_t s) {
+    const size_t words = ((size_t)n_rows + 31) / 32;
+    cudaError_t e = cudaMallocAsync((void **)hotmask, (words > 0 ? words : 1) * sizeof(uint32_t), s);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(*hotmask, 0, (words > 0 ? words : 1) * sizeof(uint32_t), s)) != cudaSuccess) return e;
+    if (dRows > 0) k_hotmask_from_rid<<<(dRows + 255) / 256, 256, 0, s>>>(rId, dRows, *hotmask);
+    return cudaGetLastError();
+}
+
 void part_arrays_free(PartArrays &P, cudaStream_t s) {
     void *bufs[] = {P.xperm, P.rId, P.hotmask, P.rowPtr_dd, P.colInd_dd, P.val_dd, P.rowPtr_CD, P.colInd_CD, P.val_CD};
     for (void *b : bufs)

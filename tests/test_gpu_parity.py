@@ -239,3 +239,53 @@ def test_c4_tau_sweep_valid_and_rejected_points():
             valid += 1
     assert (valid, rejected) == (10, 6)
     h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_stored_partition_round_trip(dtype, tmp_path):
+    """save -> load into a fresh handle: same arrays, same product bits, no matrix needed."""
+    m = synth.generate("c4", n=50_000, dtype=dtype)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    a = mx.MatXtract(dtype)
+    a.upload_csr(n, n, rp, ci, val)
+    a.partition(0.5, 0.25)
+    a.set_column_space(mx.COLSPACE_PERMUTED)
+    ya = a.spmv_host(x)
+    path = tmp_path / "part.mxp"
+    a.save_partition(path)
+    da = a.download_partition()
+    b = mx.MatXtract(dtype)
+    st = b.load_partition(path)
+    assert (b.n_rows, b.n_cols, b.nnz) == (n, n, m["nnz"]) and st.active == 1
+    db = b.download_partition()
+    for k in PART_KEYS:
+        np.testing.assert_array_equal(_bits(da[k]), _bits(db[k]), err_msg=k)
+    b.set_column_space(mx.COLSPACE_PERMUTED)
+    np.testing.assert_array_equal(_bits(ya), _bits(b.spmv_host(x)))
+    b.set_column_space(mx.COLSPACE_ORIGINAL)
+    check_y(dtype, b.spmv_host(x), rp, ci, val, x)
+    with pytest.raises(mx.MxError) as e:  # the original CSR is not in the file
+        b.partition(0.25, 0.25)
+    assert e.value.status == 4
+    other = mx.MatXtract(FP16 if dtype == FP64 else FP64)
+    with pytest.raises(mx.MxError):
+        other.load_partition(path)
+    (tmp_path / "junk").write_bytes(b"not a partition")
+    with pytest.raises(mx.MxError):
+        b.load_partition(tmp_path / "junk")
+    for h in (a, b, other):
+        h.close()
+
+
+def test_tau_search_on_the_device():
+    m = synth.generate("c3", n=8 * 20_000)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(FP64)
+    h.upload_csr(n, n, rp, ci, val)
+    tc, tr, ms_best, ms_plain = h.autotune_tau(grid=4)
+    assert 0.0 <= tr <= tc < 1.0 and ms_best > 0 and ms_best <= ms_plain * 1.0001
+    # the winner is left installed
+    check_y(FP64, h.spmv_host(x), rp, ci, val, x)
+    if (tc, tr) != (0.0, 0.0):
+        assert_partition_equal(FP64, h, oracle.partition(FP64, n, n, rp, ci, val, tc, tr))
+    h.close()
