@@ -151,7 +151,7 @@ __device__ __forceinline__ int pidx(int i) {
 }
 
 template <typename V, int IPT, bool HAS_TILE, int MODE>
-__global__ void __launch_bounds__(RESID_THREADS, 1024 / RESID_THREADS)
+__global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
                  const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
                  typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz) {
