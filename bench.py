@@ -371,6 +371,8 @@ def run_ours(args):
     sampler.active.clear()
     stream.synchronize()
     sampler.stop()
+    # the product without its row logic (stream indices + values, gather x): what this matrix's index pattern allows
+    gather_floor_ms = h.stream_gather_floor(x_dev, warm=3, iters=max(10, args.steps // 10))
 
     vb = 8 if dtype == mx.FP64 else 2
     n_rows_h = n_local
@@ -443,11 +445,14 @@ def run_ours(args):
         "dd_executor": {1: "tile (tensor cores)", 2: "csr (CUDA cores)"}.get(h.dd_executor, "none"),
         "column_space": {"in_use": {1: "permuted", 2: "original"}.get(colspace[0], "n/a"),
                          "tuned_ms_permuted": colspace[1], "tuned_ms_original": colspace[2]},
+        "csr_l2_prefetch_tiles": {"resid": h.csr_prefetch[0], "dd": h.csr_prefetch[1]},
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms, "preprocess_ms_first_call": preprocess_ms_cold,
         "ms_tile_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                     "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms},
+                     "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                     "stream_gather_floor_ms": gather_floor_ms,
+                     "floor_over_step": gather_floor_ms / (ms_step if world == 1 else halves["ms_total"])},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": n_total * vb,
                 "d2h_bytes_per_step": n_total * vb},
         "gpu_launches": h.launches_per_spmv * args.steps,

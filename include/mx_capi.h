@@ -135,6 +135,15 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
  * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */
 int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile,
                   float *ms_resid, float *ms_total);
+/* L2 prefetch distance (in tiles of the CSR kernel; 0 = off) that mx_partition settled on, by timing, for the
+ * residual half and for the core-dense block when that runs as CSR.  MX_RESID_PREFETCH=<tiles> in the environment
+ * forces a distance.  No counterpart in the reference. */
+int mx_csr_prefetch(mx_handle_t h, int *resid_tiles, int *dd_tiles);
+/* Measurement aid (no counterpart in the reference): times a pass over the uploaded CSR that streams its column
+ * indices and values and gathers x for every non-zero but has no row logic and writes nothing.  *ms is the floor
+ * that the matrix's own index pattern sets for a kernel that visits the non-zeros in CSR order on this GPU; an
+ * SpMV time is to be read against it when the gathers, not HBM, bound the product. */
+int mx_stream_gather_floor(mx_handle_t h, const void *x_dev, int warm, int iters, float *ms);
 /* Executor of the core-dense block.  The reference switches between its "dense-unfold" fragment kernel and its
  * "sparse-encode" kernel on nnz and the fragment fill ratio (test/test_autotc_spmv.cpp:1507,1518).  Here:
  * MX_DD_TILE = the tensor-core fragment kernel, MX_DD_CSR = the CUDA-core CSR kernel on the same entries (the

@@ -69,6 +69,8 @@ SYMBOLS = {
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
     "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
+    "mx_csr_prefetch": (_i, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "mx_stream_gather_floor": (_i, [_vp, _vp, _i, _i, C.POINTER(C.c_float)]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_spmv_launches": (_i, [_vp]),
     "mx_set_dd_executor": (_i, [_vp, _i]),
@@ -237,6 +239,20 @@ class MatXtract:
         t, r, a = C.c_float(), C.c_float(), C.c_float()
         self._ck(lib().mx_spmv_timed(self._h, _ptr(x_dev), _ptr(y_dev), warm, iters, C.byref(t), C.byref(r), C.byref(a)))
         return {"ms_tile": t.value, "ms_resid": r.value, "ms_total": a.value}
+
+    @property
+    def csr_prefetch(self):
+        """(residual half, core-dense block) L2 prefetch distance of the CSR kernel in tiles; 0 = off."""
+        a, b = C.c_int(), C.c_int()
+        self._ck(lib().mx_csr_prefetch(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def stream_gather_floor(self, x_dev, warm=5, iters=50) -> float:
+        """ms of a pass that streams the uploaded CSR's indices and values and gathers x, with no row logic: the floor
+        the matrix's index pattern sets for a CSR-ordered kernel on this GPU."""
+        t = C.c_float()
+        self._ck(lib().mx_stream_gather_floor(self._h, _ptr(x_dev), warm, iters, C.byref(t)))
+        return t.value
 
     def set_dd_executor(self, mode: int):
         """0 = auto (by fill ratio), 1 = tensor-core tile kernel, 2 = CSR kernel on the core-dense block."""

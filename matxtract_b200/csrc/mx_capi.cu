@@ -288,6 +288,40 @@ static int tune_colspace(mx_handle_t h) {
     return MX_OK;
 }
 
+// The CSR kernel's L2 prefetch (ResidPlan::prefetch_tiles) helps or hurts with the matrix: each CSR plan in use whose
+// size rule proposes a distance is timed with and without it (its half of the product alone), and the faster stays.
+static int tune_prefetch(mx_handle_t h) {
+    if (getenv("MX_RESID_PREFETCH")) return MX_OK;  // forced by the environment
+    ResidPlan *plans[2] = {&h->resid, (h->stats.active && !h->dd_use_tile) ? &h->ddcsr : nullptr};
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    for (ResidPlan *P : plans) {
+        if (!P || P->prefetch_tiles <= 0 || P->num_tiles <= P->prefetch_tiles + 1) continue;
+        if (!e0) {
+            HCK(cudaEventCreate(&e0));
+            HCK(cudaEventCreate(&e1));
+            HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
+        }
+        const int cand[2] = {P->prefetch_tiles, 0};
+        float ms[2] = {0, 0};
+        for (int v = 0; v < 2; ++v) {
+            P->prefetch_tiles = cand[v];
+            for (int i = 0; i < 2 + 6; ++i) {
+                if (i == 2) HCK(cudaEventRecord(e0, h->stream));
+                const bool isResid = P == &h->resid;  // the half that owns the plan, alone
+                int st = spmv_enqueue(h, h->x_stage, h->y_stage, !isResid, isResid);
+                if (st != MX_OK) return st;
+            }
+            HCK(cudaEventRecord(e1, h->stream));
+            HCK(cudaEventSynchronize(e1));
+            HCK(cudaEventElapsedTime(&ms[v], e0, e1));
+        }
+        P->prefetch_tiles = ms[0] <= ms[1] ? cand[0] : 0;
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return MX_OK;
+}
+
 // Everything that follows the extraction proper (or the loading of a stored partition): execution plans of the two
 // halves, the carrier, the index arrays in original column numbering, and the choice of the execution column space.
 static int finish_partition(mx_handle_t h) {
@@ -322,6 +356,7 @@ static int finish_partition(mx_handle_t h) {
     HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
     h->planned = true;  // the tuner runs real products
     int tst = tune_colspace(h);
+    if (tst == MX_OK) tst = tune_prefetch(h);
     if (tst != MX_OK) {
         drop_plan(h);
         return tst;
@@ -355,6 +390,12 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         h->stats.sCols = h->n_cols;
         h->stats.sRows = h->n_rows;
         h->stats.nnzColS = h->nnz;
+        h->planned = true;  // the tuner runs real products
+        int tst = tune_prefetch(h);
+        if (tst != MX_OK) {
+            drop_plan(h);
+            return tst;
+        }
     } else {
         // The reference assumes a square matrix (its tau_c scan runs i < rowA over the column table,
         // test/test_autotc_spmv.cpp:1133).  A rectangular row slab (one GPU's share of a row-partitioned
@@ -731,6 +772,39 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
     if (ms_tile) *ms_tile = out[0];
     if (ms_resid) *ms_resid = out[1];
     if (ms_total) *ms_total = out[2];
+    return MX_OK;
+}
+
+int mx_csr_prefetch(mx_handle_t h, int *resid_tiles, int *dd_tiles) {
+    if (!h) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_csr_prefetch: call mx_partition first");
+    if (resid_tiles) *resid_tiles = h->resid.prefetch_tiles;
+    if (dd_tiles) *dd_tiles = h->stats.active ? h->ddcsr.prefetch_tiles : 0;
+    return MX_OK;
+}
+
+int mx_stream_gather_floor(mx_handle_t h, const void *x_dev, int warm, int iters, float *ms) {
+    if (!h || !x_dev || !ms || warm < 0 || iters <= 0) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_stream_gather_floor: call mx_upload_csr first");
+    HCK(cudaSetDevice(h->device));
+    float *sink = nullptr;
+    HCK(cudaMallocAsync((void **)&sink, sizeof(float), h->stream));
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    for (int i = 0; e == cudaSuccess && i < warm + iters; ++i) {
+        if (i == warm) e = cudaEventRecord(e0, h->stream);
+        if (e == cudaSuccess) e = stream_gather_pass(h->dtype, h->col_ind, h->val, x_dev, sink, h->nnz, h->stream);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(e1, h->stream);
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float t = 0;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t, e0, e1);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFreeAsync(sink, h->stream);
+    if (e != cudaSuccess) return h->cuda_fail(e, "mx_stream_gather_floor");
+    *ms = t / iters;
     return MX_OK;
 }
 

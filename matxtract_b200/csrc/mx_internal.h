@@ -51,6 +51,7 @@ struct ResidPlan {
     const int *col_ind = nullptr;  // [nnz]
     const void *val = nullptr;     // [nnz]
     int tile_nnz = 0, num_tiles = 0;
+    int prefetch_tiles = 0;          // L2 prefetch distance of the CSR kernel in tiles (0: off)
     int m_rows = 0, n_empty = 0;     // non-empty / empty rows
     const int *c_ptr = nullptr;      // [m_rows+1] row pointers of the non-empty rows (= row_ptr when none is empty)
     int *c_ptr_own = nullptr;        // storage of c_ptr when it is not row_ptr
@@ -144,6 +145,8 @@ void tile_arrays_free(TileArrays &T, cudaStream_t s);
 // out[i] = map[in[i]]
 cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s);
 // x_perm[i] = x[perm[i]]
+cudaError_t stream_gather_pass(int dtype, const int *col_ind, const void *val, const void *x, float *sink, int nnz,
+                               cudaStream_t s);
 cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *x_perm, int n, cudaStream_t s);
 
 inline size_t val_bytes(int dtype) { return dtype == MX_FP64 ? 8 : 2; }

@@ -289,3 +289,42 @@ def test_tau_search_on_the_device():
     if (tc, tr) != (0.0, 0.0):
         assert_partition_equal(FP64, h, oracle.partition(FP64, n, n, rp, ci, val, tc, tr))
     h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_l2_prefetch_distance_does_not_change_the_product(dtype, monkeypatch):
+    """The CSR kernel's L2 prefetch of a later tile's streams is a hint: any distance, including one that points at
+    the last full tile, leaves y bit-identical."""
+    m = synth.generate("c2", n=120_000)
+    n, rp, ci, x = m["n"], m["row_ptr"], m["col_ind"], m["x"].astype(np.float64 if dtype == FP64 else np.float16)
+    val = values(dtype, len(ci), 5)
+    ys = []
+    for dist in ("0", "1", "3", "100000"):
+        monkeypatch.setenv("MX_RESID_PREFETCH", dist)
+        h = mx.MatXtract(dtype)
+        h.upload_csr(n, n, rp, ci, val)
+        h.partition(0.3, 0.2)
+        ys.append(h.spmv_host(x))
+        assert h.device_error() == 0
+        h.close()
+    check_y(dtype, ys[0], rp, ci, val, x)
+    for y in ys[1:]:
+        np.testing.assert_array_equal(_bits(y), _bits(ys[0]))
+
+
+def test_stream_gather_floor_is_measured_below_the_product():
+    import torch
+    m = synth.generate("c2", n=400_000)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(FP16)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(0.0, 0.0)
+    x_dev = torch.from_numpy(x.view(np.int16)).cuda().view(torch.float16)
+    y_dev = torch.empty(n, dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    floor = h.stream_gather_floor(x_dev.data_ptr(), warm=2, iters=10)
+    t = h.spmv_timed(x_dev.data_ptr(), y_dev.data_ptr(), warm=2, iters=10)["ms_total"]
+    assert 0 < floor < t * 1.5   # no row logic, nothing written: cannot be much slower than the real product
+    torch.cuda.synchronize()
+    del x_dev, y_dev
+    h.close()
