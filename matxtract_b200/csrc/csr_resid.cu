@@ -151,6 +151,36 @@ __device__ __forceinline__ int pidx(int i) {
     return i + (i >> 4) * (16 / (int)sizeof(A));
 }
 
+// Programmatic dependent launch: the kernels of one product are chained so that a kernel's CTAs become resident while
+// its predecessor drains.  A chained kernel reads only what no kernel of the product writes (the matrix, x) before
+// dep_wait(); everything a predecessor produces, and every global write, comes after it.  Both instructions do
+// nothing in a kernel that was launched without the attribute or has no dependent.
+__device__ __forceinline__ void dep_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static bool chain_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("MX_CHAIN_LAUNCHES");
+        return e ? atoi(e) != 0 : true;
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, bool chained, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = chained && chain_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename V, int IPT, bool HAS_TILE, int MODE>
 __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
@@ -171,6 +201,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
 
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int base = t * T;  // nnz < 2^31, so base fits
+    dep_release();  // the fix-up launch may become resident; it waits for this grid to finish
     const int cnt = min(T, nnz - base);
 
     // ---- phase A: lane <-> consecutive non-zeros: coalesced streams, and gathers that coalesce on runs of
@@ -308,6 +339,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     else if (openToWarpStart)
         pv += cv;
     if (hasEnd) ysum[k0] += pv;  // the first row this thread closed began in earlier threads
+    dep_wait();  // from here on: global writes, and the tile half's carrier is read
     if (tid == THREADS - 1) carry[t] = sv + (upto == 0u ? cv : A(0));
     __syncthreads();
 
@@ -330,6 +362,8 @@ __global__ void resid_fixup_kernel(const int *__restrict__ cPtr, RowOut<V> out, 
     using A = typename AccOf<V>::T;
     constexpr int T = RESID_THREADS * IPT;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    dep_release();
+    dep_wait();  // needs every carry and head of the main launch
     if (i < n_empty) store_row<V, HAS_TILE, MODE>(out, emptyRow[i], A(0));
     const int t = i + 1;
     if (t >= num_tiles) return;
@@ -371,8 +405,8 @@ __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ p
 
 template <typename V>
 cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void *ytile, const uint32_t *hotmask,
-                         int mode, const int *row_map, cudaStream_t s, void *const *peers = nullptr, int n_peers = 0,
-                         long long row_offset = 0) {
+                         int mode, const int *row_map, cudaStream_t s, bool chained, void *const *peers = nullptr,
+                         int n_peers = 0, long long row_offset = 0) {
     using A = typename AccOf<V>::T;
     constexpr int IPT = ResidCfg<V>::IPT;
     const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
@@ -389,15 +423,16 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
     const int fgrid = (fwork + 127) / 128;
-#define MX_LAUNCH(HT, MD)                                                                                          \
-    do {                                                                                                           \
-        resid_kernel<V, IPT, HT, MD><<<grid, block, 0, s>>>(P.c_ptr, P.col_ind, (const V *)P.val, (const V *)x,    \
-                                                            out, P.tile_row, (A *)P.carry, (A *)P.head, P.nnz,    \
-                                                            P.prefetch_tiles);                                     \
-        if (fgrid > 0)                                                                                             \
-            resid_fixup_kernel<V, IPT, HT, MD><<<fgrid, 128, 0, s>>>(P.c_ptr, out, P.tile_row, (const A *)P.carry, \
-                                                                     (const A *)P.head, P.m_rows, P.num_tiles,    \
-                                                                     P.empty_row, P.n_empty);                     \
+    cudaError_t le = cudaSuccess;
+#define MX_LAUNCH(HT, MD)                                                                                           \
+    do {                                                                                                            \
+        le = launch_chained(resid_kernel<V, IPT, HT, MD>, grid, block, s, chained, P.c_ptr, P.col_ind,              \
+                            (const V *)P.val, (const V *)x, out, (const int *)P.tile_row, (A *)P.carry,            \
+                            (A *)P.head, P.nnz, P.prefetch_tiles);                                                  \
+        if (le == cudaSuccess && fgrid > 0)                                                                         \
+            le = launch_chained(resid_fixup_kernel<V, IPT, HT, MD>, dim3(fgrid), dim3(128), s, true, P.c_ptr, out,  \
+                                (const int *)P.tile_row, (const A *)P.carry, (const A *)P.head, P.m_rows,           \
+                                P.num_tiles, (const int *)P.empty_row, P.n_empty);                                  \
     } while (0)
     if (mode == OUT_CARRIER)
         MX_LAUNCH(false, OUT_CARRIER);
@@ -414,7 +449,7 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     else
         MX_LAUNCH(false, OUT_Y);
 #undef MX_LAUNCH
-    return cudaGetLastError();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 }  // namespace
@@ -495,24 +530,27 @@ void resid_plan_free(ResidPlan &P, cudaStream_t s) {
 int resid_launches(const ResidPlan &P) { return (P.num_tiles > 1 || P.n_empty > 0) ? 2 : 1; }
 
 cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, const void *ytile,
-                       const uint32_t *hotmask, bool accumulate, int *, cudaStream_t s) {
+                       const uint32_t *hotmask, bool accumulate, int *, cudaStream_t s, bool chained) {
     const int mode = accumulate ? OUT_Y_ACCUM : OUT_Y;
-    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, mode, nullptr, s);
-    return resid_spmv_t<__half>(P, x, y, ytile, hotmask, mode, nullptr, s);
+    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, mode, nullptr, s, chained);
+    return resid_spmv_t<__half>(P, x, y, ytile, hotmask, mode, nullptr, s, chained);
 }
 
 cudaError_t resid_spmv_peers(int dtype, const ResidPlan &P, const void *x, void *const *peers, int n_peers,
-                             long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s) {
+                             long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
+                             bool chained) {
     if (n_peers < 1 || n_peers > MAX_PEERS) return cudaErrorInvalidValue;
     if (dtype == MX_FP64)
-        return resid_spmv_t<double>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, peers, n_peers, row_offset);
-    return resid_spmv_t<__half>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, peers, n_peers, row_offset);
+        return resid_spmv_t<double>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, chained, peers, n_peers,
+                                    row_offset);
+    return resid_spmv_t<__half>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, chained, peers, n_peers,
+                                row_offset);
 }
 
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, void *carrier, const int *row_map,
                                   cudaStream_t s) {
-    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
-    return resid_spmv_t<__half>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s);
+    if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s, false);
+    return resid_spmv_t<__half>(P, x, carrier, nullptr, nullptr, OUT_CARRIER, row_map, s, false);
 }
 
 cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s) {
@@ -696,8 +734,8 @@ extern "C" int mx_csr_spmv_static(int dtype, int n_rows, int n_cols, int nnz, co
                                                                   P.tile_row);
     STCK(cudaGetLastError());
     cudaError_t e = dtype == MX_FP64
-                        ? resid_spmv_t<double>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s)
-                        : resid_spmv_t<__half>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s);
+                        ? resid_spmv_t<double>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s, false)
+                        : resid_spmv_t<__half>(P, x_dev, y_dev, nullptr, nullptr, OUT_Y, nullptr, s, false);
     STCK(e);
 #undef STCK
     return MX_OK;

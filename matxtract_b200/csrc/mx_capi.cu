@@ -239,7 +239,8 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
             HCK(dd_enqueue(h, x));
         }
         HCK(resid_spmv_peers(h->dtype, h->resid, x, peers, n_peers, row_offset, h->stats.active ? h->ytile : nullptr,
-                             h->stats.active ? h->part.hotmask : nullptr, h->stream));
+                             h->stats.active ? h->part.hotmask : nullptr, h->stream,
+                             h->stats.active != 0 && !h->dd_use_tile));
         return MX_OK;
     }
     if (h->stats.active) {
@@ -250,7 +251,8 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         }
         if (do_tile) HCK(dd_enqueue(h, x));
         if (do_resid)
-            HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->dev_err, h->stream));
+            HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->dev_err, h->stream,
+                           /*chained=*/do_tile && !h->dd_use_tile));
     } else if (do_resid) {
         HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->dev_err, h->stream));
     }

@@ -115,14 +115,18 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &plan, cudaStream_t s);
 void resid_plan_free(ResidPlan &plan, cudaStream_t s);
 // y[r] = sum_r (+ y_in[r] when accumulate) (+ ytile[r] for rows flagged in hotmask).  ytile is of the
 // accumulate type (float for FP16, double for FP64); hotmask has one bit per row.
+// chained: the launch directly follows, on the same stream, the CSR launches of the same product's core-dense block
+// (which do not write x); the kernel's first wave may then start while they drain.  Measured: -9 % on the power-law
+// benchmark shape.  Behind the tensor-core tile kernel the same overlap costs 13 %, so it is not used there.
 cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y, const void *ytile,
-                       const uint32_t *hotmask, bool accumulate, int *dev_err, cudaStream_t s);
+                       const uint32_t *hotmask, bool accumulate, int *dev_err, cudaStream_t s, bool chained = false);
 // carrier[row_map[r]] = sum_r in the accumulate type: runs the core-dense block as CSR (low-fill dispatch)
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &plan, const void *x, void *carrier, const int *row_map,
                                   cudaStream_t s);
 // y_peer[g][row_offset + r] = row r for every g < n_peers (peer-mapped full-length y of every GPU): fused all-gather
 cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, void *const *peers, int n_peers,
-                             long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s);
+                             long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
+                             bool chained = false);
 int resid_launches(const ResidPlan &plan);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
