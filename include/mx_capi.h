@@ -135,6 +135,15 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
  * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */
 int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile,
                   float *ms_resid, float *ms_total);
+/* Matrix Market coordinate file -> host CSR with the result of the reference's mmio_allinone
+ * (utilities/mmio.cpp:1547-1713: rows in file order, `symmetric`/`hermitian` storage mirrored, pattern = 1, complex =
+ * real part, double -> value type in one rounding), parsed by `threads` host threads (<= 0: all).  Host-only: works
+ * without a GPU.  row_ptr / col_ind / val are malloc'ed; release them with free() or mx_host_free().  Returns 0 or
+ * the reference's codes: -1 cannot open, -2 banner, -4 size line / entries, -5 more than INT_MAX stored entries or
+ * out of memory, -3 bad argument. */
+int mx_read_matrix_market(const char *path, int dtype, int threads, int *rows, int *cols, int *nnz, int *is_symmetric,
+                          int **row_ptr, int **col_ind, void **val);
+void mx_host_free(void *p);
 /* L2 prefetch distance (in tiles of the CSR kernel; 0 = off) that mx_partition settled on, by timing, for the
  * residual half and for the core-dense block when that runs as CSR.  MX_RESID_PREFETCH=<tiles> in the environment
  * forces a distance.  No counterpart in the reference. */

@@ -19,8 +19,9 @@ from .capi import (  # noqa: F401
     cdspmv,
     du_tcspmv,
     lib,
+    read_matrix_market,
     se_tcspmv,
 )
 from . import synth  # noqa: F401
 
-__all__ = ["FP16", "FP64", "MatXtract", "MxError", "PartitionStats", "cdspmv", "du_tcspmv", "se_tcspmv", "lib", "synth"]
+__all__ = ["FP16", "FP64", "MatXtract", "MxError", "PartitionStats", "cdspmv", "du_tcspmv", "se_tcspmv", "lib", "read_matrix_market", "synth"]

@@ -69,6 +69,10 @@ SYMBOLS = {
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
     "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
+    "mx_read_matrix_market": (_i, [C.c_char_p, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                   C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
+                                   C.POINTER(_vp)]),
+    "mx_host_free": (None, [_vp]),
     "mx_csr_prefetch": (_i, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mx_stream_gather_floor": (_i, [_vp, _vp, _i, _i, C.POINTER(C.c_float)]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
@@ -293,6 +297,28 @@ class MatXtract:
 def _raise(st):
     if st != 0:
         raise MxError(st, lib().mx_status_string(st).decode())
+
+
+def read_matrix_market(path, dtype: int, threads: int = 0):
+    """Matrix Market coordinate file -> (rows, cols, row_ptr, col_ind, val, is_symmetric), host arrays, parsed by
+    `threads` host threads (0 = all).  Same CSR as the reference's ``mmio_allinone``.  Needs no GPU."""
+    m, n, nnz, sym = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    rp, ci, va = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.c_void_p()
+    st = lib().mx_read_matrix_market(str(path).encode(), dtype, threads, C.byref(m), C.byref(n), C.byref(nnz),
+                                     C.byref(sym), C.byref(rp), C.byref(ci), C.byref(va))
+    if st != 0:
+        raise MxError(st, f"mx_read_matrix_market({path}) failed with the reference reader's code {st}")
+    try:
+        row_ptr = np.ctypeslib.as_array(rp, (m.value + 1,)).copy()
+        col_ind = np.ctypeslib.as_array(ci, (max(nnz.value, 1),))[: nnz.value].copy()
+        vdt = np_dtype(dtype)
+        raw = (C.c_char * (max(nnz.value, 1) * np.dtype(vdt).itemsize)).from_address(va.value)
+        val = np.frombuffer(raw, dtype=vdt)[: nnz.value].copy()
+    finally:
+        lib().mx_host_free(C.cast(rp, C.c_void_p))
+        lib().mx_host_free(C.cast(ci, C.c_void_p))
+        lib().mx_host_free(va)
+    return m.value, n.value, row_ptr, col_ind, val, bool(sym.value)
 
 
 def cdspmv(dtype, val, row_ptr, col_ind, x, y, warm=0, iters=0):

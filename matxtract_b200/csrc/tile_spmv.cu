@@ -142,6 +142,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar) {
 
 constexpr int STAGE_WARPS_MAX = 8;
 int g_stage_warps = 4;           // warps per CTA (4 or 8)
+int g_tile_prefetch = -1;        // L2 prefetch distance in CTAs; default 5 per SM (A/B on the block matrix: tile half
+                                 // 113.8 -> 108.7 us; 10 per SM 110.1, 20 per SM 122.8), MX_TILE_PREFETCH overrides, 0 = off
 int g_stage_bytes = 16 * 1024;   // target bytes per CTA; a CTA may exceed it by one segment (sweep: 8-64 KB)
 
 // byte layout of a CTA's shared-memory stage; every range starts 16-byte aligned in global AND shared memory
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(STAGE_WARPS * 32)
                        const int4 *__restrict__ segDesc, const int *__restrict__ panelFirstSeg,
                        typename std::conditional<sizeof(V) == 8, double, float>::type *__restrict__ partial,
                        unsigned *__restrict__ panelCount, OutT *__restrict__ out, const int *__restrict__ row_map,
-                       int dRows, int *__restrict__ devErr) {
+                       int dRows, int *__restrict__ devErr, int prefetchCtas) {
     extern __shared__ __align__(16) unsigned char stage[];
     uint64_t *bar = reinterpret_cast<uint64_t *>(stage);
     const CtaDesc d = desc[blockIdx.x];
@@ -283,6 +285,20 @@ __global__ void __launch_bounds__(STAGE_WARPS * 32)
         if (L.nBit) bulk_g2s(stage + L.oBit, fragBit + L.fa, L.nBit, bar);
         if (L.nPtr) bulk_g2s(stage + L.oPtr, fragPtr + L.fa, L.nPtr, bar);
         if (L.nV) bulk_g2s(stage + L.oV, tcVal + L.va, L.nV, bar);
+    }
+    if (prefetchCtas > 0 && blockIdx.x + prefetchCtas < gridDim.x) {
+        // while this stage is in flight: ask L2 for the stage of the CTA one wave ahead
+        const CtaDesc dn = desc[blockIdx.x + prefetchCtas];
+        const StageLayout<B, V, K> Ln(dn.f0, dn.f1, dn.v0, dn.v1);
+        const char *base[4] = {reinterpret_cast<const char *>(AToX + (size_t)dn.f0 * K),
+                               reinterpret_cast<const char *>(fragBit + Ln.fa),
+                               reinterpret_cast<const char *>(fragPtr + Ln.fa),
+                               reinterpret_cast<const char *>(tcVal + Ln.va)};
+        const uint32_t len[4] = {Ln.nX, Ln.nBit, Ln.nPtr, Ln.nV};
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            for (uint32_t off = threadIdx.x * 128u; off < len[r]; off += STAGE_WARPS * 32 * 128u)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(base[r] + off));
     }
     if (!mbar_wait_bounded(bar)) {  // never expected; leaves a mark instead of spinning for ever
         if (lane == 0 && devErr) atomicOr(devErr, DEVERR_TILE_RANGE);
@@ -433,6 +449,14 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
     if (const char *ev = getenv("MX_STAGE_BYTES")) g_stage_bytes = atoi(ev);
     if (const char *ev = getenv("MX_STAGE_WARPS")) g_stage_warps = atoi(ev) == 4 ? 4 : 8;
+    if (const char *ev = getenv("MX_TILE_PREFETCH")) {
+        g_tile_prefetch = atoi(ev) > 0 ? atoi(ev) : 0;
+    } else if (g_tile_prefetch < 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        g_tile_prefetch = 5 * sms;
+    }
     const int STAGE_BYTES = g_stage_bytes;
     P.numCtas = (int)((totalBytes + STAGE_BYTES - 1) / STAGE_BYTES);
     if (P.numCtas < 1) P.numCtas = 1;
@@ -488,7 +512,7 @@ cudaError_t tile_spmv(int dtype, const TilePlan &P, const void *x_d, void *out, 
         kern<<<sg, sb, smem, s>>>((const VT *)x_d, P.A.fragPtr, (const BT *)P.A.fragBit, (const VT *)P.A.tcVal,      \
                                   P.A.AToX, (const CtaDesc *)P.ctaDesc, (const int4 *)P.segDesc,                     \
                                   P.panelFirstSeg, (AT *)P.partial, P.panelCount, (OT *)out, row_map, P.A.dRows,     \
-                                  dev_err);                                                                          \
+                                  dev_err, g_tile_prefetch);                                                         \
     } while (0)
         if (dtype == MX_FP64) {
             if (accumulate)
