@@ -135,6 +135,23 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
  * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */
 int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int iters, float *ms_tile,
                   float *ms_resid, float *ms_total);
+/* Structure features of the uploaded matrix: the statistics of its non-zeros-per-row and non-zeros-per-column
+ * distributions that the reference's tau predictor takes as input (ML/extract_features.cpp:19-93; CSV columns
+ * rowMean ... rowHot90, colMean ... colHot90 of :112-119), computed on the device.  top[] = k-th largest count / mean
+ * for k = 1,2,3,4,5,10,50,100,200,300; hot[] = fraction of rows (columns) that holds 10 %, 20 %, ... 90 % of the
+ * non-zeros when taken in descending order. */
+typedef struct {
+    double mean, std_dev;
+    long long min, max;
+    double p_ratio;
+    double top[10];
+    double hot[9];
+} mx_dist_features;
+typedef struct {
+    long long rows, cols, nnz;
+    mx_dist_features row, col;
+} mx_matrix_features;
+int mx_features(mx_handle_t h, mx_matrix_features *out);
 /* Matrix Market coordinate file -> host CSR with the result of the reference's mmio_allinone
  * (utilities/mmio.cpp:1547-1713: rows in file order, `symmetric`/`hermitian` storage mirrored, pattern = 1, complex =
  * real part, double -> value type in one rounding), parsed by `threads` host threads (<= 0: all).  Host-only: works

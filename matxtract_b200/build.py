@@ -83,6 +83,12 @@ def build_all(verbose: bool = False, force: bool = False, ptxas_info: bool = Fal
                       "-I/usr/local/cuda/include", *srcs, f"-L{LIBDIR}", f"-lMatXtract_{tag}", "-lmatxtract_b200",
                       "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64",
                       "-o", exe], verbose)
+        feat = host / "extract_features.cpp"
+        exe = LIBDIR / "extract_features"
+        if feat.exists() and (force or _newer(feat, exe, headers) or _newer(LIB, exe)):
+            _run(["/usr/bin/g++", "-std=c++17", "-O2", f"-I{ROOT / 'include'}", feat, f"-L{LIBDIR}", "-lmatxtract_b200",
+                  "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64",
+                  "-o", exe], verbose)
     probe = CSRC / "probe" / "gather_ceiling.cu"
     exe = LIBDIR / "gather_ceiling"
     if probe.exists() and (force or _newer(probe, exe)):

@@ -24,6 +24,21 @@ class MxError(RuntimeError):
         super().__init__(f"{STATUS.get(status, status)}: {msg}")
 
 
+class DistFeatures(C.Structure):
+    _fields_ = [("mean", C.c_double), ("std_dev", C.c_double), ("min", C.c_longlong), ("max", C.c_longlong),
+                ("p_ratio", C.c_double), ("top", C.c_double * 10), ("hot", C.c_double * 9)]
+
+    def as_array(self) -> np.ndarray:
+        """mean, std, min, max, pRatio, top1..top300, hot10..hot90: the reference's CSV column order."""
+        return np.array([self.mean, self.std_dev, float(self.min), float(self.max), self.p_ratio,
+                         *self.top, *self.hot], np.float64)
+
+
+class MatrixFeatures(C.Structure):
+    _fields_ = [("rows", C.c_longlong), ("cols", C.c_longlong), ("nnz", C.c_longlong),
+                ("row", DistFeatures), ("col", DistFeatures)]
+
+
 class PartitionStats(C.Structure):
     _fields_ = [("dCols", C.c_int), ("nnzColD", C.c_int), ("sCols", C.c_int), ("nnzColS", C.c_int),
                 ("dRows", C.c_int), ("nnzRowD", C.c_int), ("sRows", C.c_int), ("nnzRowS", C.c_int),
@@ -73,6 +88,7 @@ SYMBOLS = {
                                    C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
                                    C.POINTER(_vp)]),
     "mx_host_free": (None, [_vp]),
+    "mx_features": (_i, [_vp, _vp]),
     "mx_csr_prefetch": (_i, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mx_stream_gather_floor": (_i, [_vp, _vp, _i, _i, C.POINTER(C.c_float)]),
     "mx_spmv_timed": (_i, [_vp, _vp, _vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
@@ -243,6 +259,12 @@ class MatXtract:
         t, r, a = C.c_float(), C.c_float(), C.c_float()
         self._ck(lib().mx_spmv_timed(self._h, _ptr(x_dev), _ptr(y_dev), warm, iters, C.byref(t), C.byref(r), C.byref(a)))
         return {"ms_tile": t.value, "ms_resid": r.value, "ms_total": a.value}
+
+    def features(self) -> MatrixFeatures:
+        """Row / column distribution statistics of the uploaded matrix (the reference's ML feature vector)."""
+        f = MatrixFeatures()
+        self._ck(lib().mx_features(self._h, C.byref(f)))
+        return f
 
     @property
     def csr_prefetch(self):

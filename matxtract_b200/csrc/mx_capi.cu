@@ -777,6 +777,21 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
     return MX_OK;
 }
 
+int mx_features(mx_handle_t h, mx_matrix_features *out) {
+    if (!h || !out) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_features: call mx_upload_csr first");
+    HCK(cudaSetDevice(h->device));
+    CsrDev A;
+    A.n_rows = h->n_rows;
+    A.n_cols = h->n_cols;
+    A.nnz = h->nnz;
+    A.row_ptr = h->row_ptr;
+    A.col_ind = h->col_ind;
+    A.val = h->val;
+    HCK(matrix_features(A, *out, h->stream));
+    return MX_OK;
+}
+
 int mx_csr_prefetch(mx_handle_t h, int *resid_tiles, int *dd_tiles) {
     if (!h) return MX_ERR_INVALID;
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_csr_prefetch: call mx_partition first");

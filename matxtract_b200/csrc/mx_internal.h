@@ -149,6 +149,7 @@ void tile_arrays_free(TileArrays &T, cudaStream_t s);
 // out[i] = map[in[i]]
 cudaError_t map_indices(const int *in, const int *map, int *out, long long n, cudaStream_t s);
 // x_perm[i] = x[perm[i]]
+cudaError_t matrix_features(const CsrDev &A, mx_matrix_features &out, cudaStream_t s);
 cudaError_t stream_gather_pass(int dtype, const int *col_ind, const void *val, const void *x, float *sink, int nnz,
                                cudaStream_t s);
 cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *x_perm, int n, cudaStream_t s);

@@ -57,6 +57,8 @@ def olib():
         L.mxo_init_vec.argtypes = [C.c_int, _vp, C.c_int]
         L.mxo_eqcheck.restype = C.c_int
         L.mxo_eqcheck.argtypes = [C.c_int, _vp, _vp, C.c_int]
+        L.mxo_dist_stats.restype = None
+        L.mxo_dist_stats.argtypes = [_vp, C.c_longlong, _vp]
         L.mxo_abs_rowsum_max.restype = C.c_double
         L.mxo_abs_rowsum_max.argtypes = [C.c_int, _vp, _vp, _vp, _vp, C.c_int]
         _olib = L
@@ -171,6 +173,36 @@ def exact_spmv(row_ptr, col_ind, val, x):
 # The reference's own host code (oracle/_ref).  Only available where it was built (needs the reference sources).
 # ---------------------------------------------------------------------------------------------------
 _rlibs = {}
+
+
+FEATURE_NAMES = (["Mean", "Std", "Min", "Max", "PRatio"] + [f"Top{k}" for k in (1, 2, 3, 4, 5, 10, 50, 100, 200, 300)]
+                 + [f"Hot{p}" for p in range(10, 100, 10)])
+
+
+def dist_stats(counts) -> np.ndarray:
+    """The 24 statistics of one count distribution, in the order of FEATURE_NAMES (ML/extract_features.cpp:19-93)."""
+    a = np.ascontiguousarray(counts, np.int64)
+    out = np.zeros(24, np.float64)
+    olib().mxo_dist_stats(_p(a), len(a), _p(out))
+    return out
+
+
+def matrix_features(n_rows, n_cols, row_ptr, col_ind) -> dict:
+    """Row and column distributions formed as in ML/extract_features.cpp:155-170."""
+    rows = np.diff(np.asarray(row_ptr, np.int64))[:n_rows]
+    cols = np.bincount(np.asarray(col_ind, np.int64), minlength=n_cols)[:n_cols] if n_cols else np.zeros(0, np.int64)
+    return {"row": dist_stats(rows), "col": dist_stats(cols)}
+
+
+def ref_dist_stats(counts) -> np.ndarray:
+    """The reference's own computeDistStats (compiled from its source into oracle/_ref)."""
+    L = rlib(FP64)
+    L.ref_dist_stats.restype = None
+    L.ref_dist_stats.argtypes = [_vp, C.c_longlong, _vp]
+    a = np.ascontiguousarray(counts, np.int64)
+    out = np.zeros(24, np.float64)
+    L.ref_dist_stats(_p(a), len(a), _p(out))
+    return out
 
 
 def ref_available() -> bool:

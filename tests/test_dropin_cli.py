@@ -67,3 +67,39 @@ def test_reference_driver_source_runs_on_this_library(tag, tau, mtx):
     assert r.returncode == 0, r.stderr
     assert "Success! All values match within the tolerance for 300 elements." in r.stdout
     assert "MatXtract time = " in r.stdout
+
+
+def test_extract_features_usage_without_arguments():
+    r = run([LIB / "extract_features"])
+    assert r.returncode == 1 and "<mtx_root_folder> <output_csv>" in r.stderr
+
+
+@pytest.mark.gpu
+def test_extract_features_writes_the_reference_csv(tmp_path):
+    """ML/extract_features.cpp:95-217: one row per <root>/<name>/<name>.mtx, the reference's header, default stream
+    formatting (6 significant digits)."""
+    import csv
+
+    cases = {c[0]: c for c in small_cases()}
+    root = tmp_path / "root"
+    for name in ("skew300", "powerlaw500"):
+        _, n, rp, ci = cases[name]
+        (root / name).mkdir(parents=True)
+        oracle.write_mtx(root / name / f"{name}.mtx", n, n, rp, ci)
+    (root / "stray.txt").write_text("not a folder")
+    out = tmp_path / "features.csv"
+    r = run([LIB / "extract_features", root, out])
+    assert r.returncode == 0, r.stderr
+    assert f"Feature extraction done. Results saved to {out}" in r.stdout
+    rows = list(csv.reader(out.open()))
+    header = rows[0]
+    assert header[:9] == ["MatrixName", "nrows", "ncols", "nnz", "rowMean", "rowStd", "rowMin", "rowMax", "rowPRatio"]
+    assert len(header) == 4 + 48 and header[-1] == "colHot90" and header[28] == "colMean"
+    got = {r[0]: r for r in rows[1:]}
+    assert set(got) == {"skew300", "powerlaw500"}
+    for name, rec in got.items():
+        _, n, rp, ci = cases[name]
+        o = oracle.matrix_features(n, n, rp, ci)
+        assert [int(v) for v in rec[1:4]] == [n, n, len(ci)]
+        np.testing.assert_allclose([float(v) for v in rec[4:28]], o["row"], rtol=1e-5, atol=1e-12)
+        np.testing.assert_allclose([float(v) for v in rec[28:52]], o["col"], rtol=1e-5, atol=1e-12)
