@@ -371,6 +371,33 @@ def run_ours(args):
     sampler.active.clear()
     stream.synchronize()
     sampler.stop()
+    # library comparator on the same GPU and matrix: cuSPARSE CSR SpMV (through torch.mv on a sparse-CSR tensor)
+    cusparse = None
+    if world == 1 and not args.no_library_baseline and nnz_total <= 300_000_000:  # a second copy of the CSR
+        try:
+            with torch.cuda.stream(stream):
+                A = torch.sparse_csr_tensor(
+                    torch.from_numpy(m["row_ptr"].astype(np.int32)).to(f"cuda:{local}"),
+                    torch.from_numpy(m["col_ind"].astype(np.int32)).to(f"cuda:{local}"),
+                    torch.from_numpy(m["val"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).to(f"cuda:{local}"),
+                    size=(n_local, n_total))
+                y_lib = torch.mv(A, x_dev)
+                k = max(10, args.steps // 5)
+                for _ in range(3):
+                    torch.mv(A, x_dev, out=y_lib)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(k):
+                    torch.mv(A, x_dev, out=y_lib)
+                e1.record(stream)
+            stream.synchronize()
+            ms_lib = e0.elapsed_time(e1) / k
+            err_lib = float((y_lib.double() - y_full.double()).abs().max() / y_full.double().abs().max().clamp_min(1e-30))
+            cusparse = {"kind": "cuSPARSE CSR SpMV via torch.mv, same GPU, same matrix and x", "ms": ms_lib,
+                        "gflops": 2.0 * nnz_total / (ms_lib * 1e-3) / 1e9, "max_rel_diff_to_ours": err_lib}
+            del A, y_lib
+        except Exception as e:  # comparator only: never fails the run
+            cusparse = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     # the product without its row logic (stream indices + values, gather x): what this matrix's index pattern allows
     gather_floor_ms = h.stream_gather_floor(x_dev, warm=3, iters=max(10, args.steps // 10))
 
@@ -458,6 +485,8 @@ def run_ours(args):
         "gpu_launches": h.launches_per_spmv * args.steps,
         "clocks": sampler.summary(),
     }
+    if cusparse is not None:
+        line["library_baseline"] = cusparse
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
@@ -470,6 +499,7 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-library-baseline", action="store_true", help="skip the cuSPARSE comparator")
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--n", "--rows", dest="n", type=int, default=0,
                     help="rows per GPU (default: the configuration's size); spell it --rows under torchrun")

@@ -69,6 +69,20 @@ def test_reference_driver_source_runs_on_this_library(tag, tau, mtx):
     assert "MatXtract time = " in r.stdout
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["fp64", "fp16"])
+def test_reference_cdspmv_driver_source_runs_on_this_library(tag, mtx):
+    """The reference's second driver (test/test_cdspmv.cpp, its cuda_perftest target: cdspmv timed beside cuSPARSE and
+    checked against its serial product), compiled unmodified and linked against this library's cdspmv."""
+    exe = ROOT / "oracle" / "_ref" / f"reference_cdspmv_{tag}"
+    if not exe.exists():
+        pytest.skip("oracle/_ref/reference_cdspmv_* not built (needs the reference sources)")
+    r = run([exe, mtx])
+    assert r.returncode == 0, r.stderr
+    assert "cd_perf:" in r.stdout and "our_pre:" in r.stdout and "cusparse_perf:" in r.stdout
+    assert "Success! All values match within the tolerance for 300 elements." in r.stdout
+
+
 def test_extract_features_usage_without_arguments():
     r = run([LIB / "extract_features"])
     assert r.returncode == 1 and "<mtx_root_folder> <output_csv>" in r.stderr
