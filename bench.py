@@ -416,9 +416,11 @@ def run_ours(args):
     # DRAM read + write bytes of the dominant kernel per launch, from the ncu captures summarised under profiles/
     # (resid_kernel_c2_fp16.md, tile_and_resid_kernels_c3_fp64.md); null for workloads that were not captured
     traffic = None
-    if world == 1 and not args.n and not args.tau:
-        traffic = {("c2", "resid_kernel(+fixup)"): 137.4e6, ("c3", "resid_kernel(+fixup)"): 643.1e6,
-                   ("c3", "tile_kernel"): 479.4e6}.get((cfg.name, dom))
+    if world == 1 and not args.n:
+        tau_key = "default" if not args.tau else ("tau0" if tuple(args.tau) == (0.0, 0.0) else None)
+        traffic = {("c2", "resid_kernel(+fixup)", "default"): 136.5e6, ("c3", "resid_kernel(+fixup)", "default"): 645.7e6,
+                   ("c3", "tile_kernel", "default"): 489.1e6,
+                   ("c3", "resid_kernel(+fixup)", "tau0"): 1240.9e6}.get((cfg.name, dom, tau_key))
     eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
 
     def shutdown():
