@@ -57,6 +57,19 @@ struct mx_handle_s {
 
 namespace {
 
+// two timing events that are destroyed on every way out of a function
+struct EventPair {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t create() {
+        cudaError_t e = cudaEventCreate(&e0);
+        return e == cudaSuccess ? cudaEventCreate(&e1) : e;
+    }
+    ~EventPair() {
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+    }
+};
+
 void drop_plan(mx_handle_t h) {
     cudaStream_t s = h->stream;  // frees are ordered after whatever the stream still has in flight
     resid_plan_free(h->resid, s);
@@ -266,9 +279,9 @@ static int tune_colspace(mx_handle_t h) {
         select_colspace(h, h->colspace_mode == MX_COLSPACE_ORIGINAL);
         return MX_OK;
     }
-    cudaEvent_t e0, e1;
-    HCK(cudaEventCreate(&e0));
-    HCK(cudaEventCreate(&e1));
+    EventPair ev;
+    HCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
     float ms[2] = {0, 0};
     for (int space = 0; space < 2; ++space) {
@@ -282,8 +295,6 @@ static int tune_colspace(mx_handle_t h) {
         HCK(cudaEventSynchronize(e1));
         HCK(cudaEventElapsedTime(&ms[space], e0, e1));
     }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     h->tune_ms_perm = ms[0] / 10;
     h->tune_ms_orig = ms[1] / 10;
     select_colspace(h, ms[1] < ms[0]);
@@ -295,12 +306,11 @@ static int tune_colspace(mx_handle_t h) {
 static int tune_prefetch(mx_handle_t h) {
     if (getenv("MX_RESID_PREFETCH")) return MX_OK;  // forced by the environment
     ResidPlan *plans[2] = {&h->resid, (h->stats.active && !h->dd_use_tile) ? &h->ddcsr : nullptr};
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    EventPair ev;
     for (ResidPlan *P : plans) {
         if (!P || P->prefetch_tiles <= 0 || P->num_tiles <= P->prefetch_tiles + 1) continue;
-        if (!e0) {
-            HCK(cudaEventCreate(&e0));
-            HCK(cudaEventCreate(&e1));
+        if (!ev.e0) {
+            HCK(ev.create());
             HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
         }
         const int cand[2] = {P->prefetch_tiles, 0};
@@ -308,19 +318,17 @@ static int tune_prefetch(mx_handle_t h) {
         for (int v = 0; v < 2; ++v) {
             P->prefetch_tiles = cand[v];
             for (int i = 0; i < 2 + 6; ++i) {
-                if (i == 2) HCK(cudaEventRecord(e0, h->stream));
+                if (i == 2) HCK(cudaEventRecord(ev.e0, h->stream));
                 const bool isResid = P == &h->resid;  // the half that owns the plan, alone
                 int st = spmv_enqueue(h, h->x_stage, h->y_stage, !isResid, isResid);
                 if (st != MX_OK) return st;
             }
-            HCK(cudaEventRecord(e1, h->stream));
-            HCK(cudaEventSynchronize(e1));
-            HCK(cudaEventElapsedTime(&ms[v], e0, e1));
+            HCK(cudaEventRecord(ev.e1, h->stream));
+            HCK(cudaEventSynchronize(ev.e1));
+            HCK(cudaEventElapsedTime(&ms[v], ev.e0, ev.e1));
         }
         P->prefetch_tiles = ms[0] <= ms[1] ? cand[0] : 0;
     }
-    if (e0) cudaEventDestroy(e0);
-    if (e1) cudaEventDestroy(e1);
     return MX_OK;
 }
 
@@ -373,9 +381,9 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
     HCK(cudaSetDevice(h->device));
     drop_plan(h);
     const float colProp = (float)tau_c, rowProp = (float)tau_r;
-    cudaEvent_t e0, e1;
-    HCK(cudaEventCreate(&e0));
-    HCK(cudaEventCreate(&e1));
+    EventPair ev;
+    HCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     HCK(cudaEventRecord(e0, h->stream));
     h->stats = mx_partition_stats{};
     h->stats.fragK = frag_k(h->dtype);
@@ -427,8 +435,6 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
     HCK(cudaEventSynchronize(e1));
     float ms = 0;
     HCK(cudaEventElapsedTime(&ms, e0, e1));
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     h->stats.preprocess_ms = ms;
     h->planned = true;
     if (stats) *stats = h->stats;
@@ -577,9 +583,9 @@ int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float
     if (!h || grid < 1 || grid > 16 || !tau_c || !tau_r) return MX_ERR_INVALID;
     if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_autotune_tau: no matrix uploaded");
     HCK(cudaSetDevice(h->device));
-    cudaEvent_t e0, e1;
-    HCK(cudaEventCreate(&e0));
-    HCK(cudaEventCreate(&e1));
+    EventPair ev;
+    HCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     double bc = 0, br = 0;
     float best = -1.f, plain = 0.f;
     for (int i = 0; i < grid; ++i)
@@ -607,8 +613,6 @@ int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float
                 br = tr;
             }
         }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     int st = mx_partition(h, bc, br, nullptr);
     if (st != MX_OK) return st;
     *tau_c = bc;
@@ -743,9 +747,9 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
     if (!h || !x_dev || !y_dev || warm < 0 || iters <= 0) return MX_ERR_INVALID;
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_timed: call mx_partition first");
     HCK(cudaSetDevice(h->device));
-    cudaEvent_t e0, e1;
-    HCK(cudaEventCreate(&e0));
-    HCK(cudaEventCreate(&e1));
+    EventPair ev;
+    HCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     float out[3] = {0, 0, 0};
     for (int phase = 0; phase < 3; ++phase) {
         const bool do_tile = phase != 1, do_resid = phase != 0;
@@ -769,8 +773,6 @@ int mx_spmv_timed(mx_handle_t h, const void *x_dev, void *y_dev, int warm, int i
         HCK(cudaEventElapsedTime(&ms, e0, e1));
         out[phase] = ms / iters;
     }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     if (ms_tile) *ms_tile = out[0];
     if (ms_resid) *ms_resid = out[1];
     if (ms_total) *ms_total = out[2];
@@ -806,9 +808,9 @@ int mx_stream_gather_floor(mx_handle_t h, const void *x_dev, int warm, int iters
     HCK(cudaSetDevice(h->device));
     float *sink = nullptr;
     HCK(cudaMallocAsync((void **)&sink, sizeof(float), h->stream));
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    cudaError_t e = cudaEventCreate(&e0);
-    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    EventPair ev;
+    cudaError_t e = ev.create();
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     for (int i = 0; e == cudaSuccess && i < warm + iters; ++i) {
         if (i == warm) e = cudaEventRecord(e0, h->stream);
         if (e == cudaSuccess) e = stream_gather_pass(h->dtype, h->col_ind, h->val, x_dev, sink, h->nnz, h->stream);
@@ -817,8 +819,6 @@ int mx_stream_gather_floor(mx_handle_t h, const void *x_dev, int warm, int iters
     if (e == cudaSuccess) e = cudaEventSynchronize(e1);
     float t = 0;
     if (e == cudaSuccess) e = cudaEventElapsedTime(&t, e0, e1);
-    if (e0) cudaEventDestroy(e0);
-    if (e1) cudaEventDestroy(e1);
     cudaFreeAsync(sink, h->stream);
     if (e != cudaSuccess) return h->cuda_fail(e, "mx_stream_gather_floor");
     *ms = t / iters;
@@ -863,9 +863,9 @@ int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *cs
     P.row_ptr = d_ptr;
     P.col_ind = d_ind;
     P.val = d_val;
-    cudaEvent_t e0, e1;
-    SCK(cudaEventCreate(&e0));
-    SCK(cudaEventCreate(&e1));
+    EventPair ev;
+    SCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     SCK(cudaEventRecord(e0, 0));
     cudaError_t ce = resid_plan_build(dtype, P, 0);
     SCK(cudaEventRecord(e1, 0));
@@ -886,8 +886,6 @@ int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *cs
         if (ce == cudaSuccess) ce = cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost);
     }
     resid_plan_free(P, 0);
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     SCK(ce);
     return MX_OK;
 }
@@ -897,9 +895,9 @@ static int run_tiles(int dtype, TileArrays &T, const void *d_x, void *d_y, void 
     TilePlan P;
     P.A = T;
     cudaError_t ce = tile_plan_build(dtype, P, 0);
-    cudaEvent_t e0, e1;
-    cudaEventCreate(&e0);
-    cudaEventCreate(&e1);
+    EventPair ev;
+    SCK(ev.create());
+    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     for (int i = 0; i < warm + iters && ce == cudaSuccess; ++i) {
         if (i == warm) cudaEventRecord(e0, 0);
         ce = tile_spmv(dtype, P, d_x, d_scratch, nullptr, false, false, nullptr, 0);
@@ -914,8 +912,6 @@ static int run_tiles(int dtype, TileArrays &T, const void *d_x, void *d_y, void 
     if (ce == cudaSuccess) ce = tile_spmv(dtype, P, d_x, d_y, nullptr, false, accumulate, nullptr, 0);
     if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
     tile_plan_free(P, 0);
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     SCK(ce);
     return MX_OK;
 }
