@@ -7,7 +7,11 @@ kernel, residual CSR kernel).  The default workload is the power-law graph confi
 FP16, tau = (0.46, 0.33)) generated from shape statistics (the reference's SuiteSparse inputs are not available
 offline).  With N > 1 (launched by torchrun, one rank per GPU) every rank owns an equal slab of rows of an
 (N*n) x (N*n) matrix of the same shape, x is replicated and y is all-gathered over NCCL inside the timed step: weak
-scaling.  Prints one JSON line (rank 0).
+scaling.  Prints one JSON line (rank 0).  Beside the contract's keys it carries, at N = 1, two comparators measured in
+the same run: "library_baseline" (cuSPARSE's CSR SpMV on the same matrix and x, through torch.mv) and
+"roofline.stream_gather_floor_ms" (a pass over the same CSR that streams indices and values and gathers x but has no
+row logic and writes nothing: what the matrix's index pattern allows a CSR-ordered kernel on this GPU), and
+"csr_l2_prefetch_tiles" (what the plan-time tuner chose for the CSR kernels).
 
 --impl reference times the reference's serial CPU SpMV (its spmv_serial, from oracle/_ref when that was built from the
 reference sources, else the oracle port) on all host cores over row slabs of a bounded sample of the same workload.
