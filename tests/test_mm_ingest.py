@@ -112,3 +112,18 @@ def test_empty_matrix_and_trailing_lines(tmp_path):
     p.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n2 1 4.0\n1 1 9.0\n")  # one line too many
     m, n, rp, ci, val, _ = mx.read_matrix_market(p, FP64)
     assert (list(rp), list(ci), list(val)) == ([0, 0, 1], [0], [4.0])
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="oracle/_ref not built (needs the reference sources)")
+@pytest.mark.parametrize("body", ["3 3 3\r\n1 1 1.5\r\n2 3 -2\r\n3 2 4e1\r\n", "3 3 3\n1 1 1.5\n2 3 -2\n3 2 4e1",
+                                  "  3\t3   3 \n   1 1   1.5\n\n2\t3 -2\n3 2 4e1\n\n"],
+                         ids=["crlf", "no_trailing_newline", "blank_lines_tabs_spaces"])
+def test_reader_line_ending_and_spacing_variants_match_reference(body, tmp_path):
+    p = tmp_path / "v.mtx"
+    p.write_bytes(("%%MatrixMarket matrix coordinate real general\n% c\n" + body).encode())
+    m, n, rp_r, ci_r, val_r = oracle.ref_read_mtx(FP64, p)
+    mm, nn, rp, ci, val, _ = mx.read_matrix_market(p, FP64, 2)
+    assert (mm, nn) == (m, n)
+    np.testing.assert_array_equal(rp, rp_r)
+    np.testing.assert_array_equal(ci, ci_r)
+    np.testing.assert_array_equal(_bits(val), _bits(val_r))
