@@ -167,7 +167,7 @@ def cpu_spmv_time(dtype, m, rows, threads, repeats):
         for t in ts:
             t.join()
         best = min(best, time.perf_counter() - t0)
-    return best, nnz, kind
+    return best, nnz, kind, y
 
 
 def run_reference(args):
@@ -179,7 +179,7 @@ def run_reference(args):
     threads = cpu_threads()
     # bounded sample: calibrate on 50k rows, then size the sample so that all steps fit in ~100 s
     probe_rows = min(n_local, 50_000)
-    t_probe, nnz_probe, kind = cpu_spmv_time(dtype, m, probe_rows, threads, 1)
+    t_probe, nnz_probe, kind, _ = cpu_spmv_time(dtype, m, probe_rows, threads, 1)
     rate = nnz_probe / max(t_probe, 1e-9)
     budget_s = 100.0
     want_nnz = rate * budget_s / max(1, args.steps + args.warmup)
@@ -189,7 +189,7 @@ def run_reference(args):
     times = []
     nnz = 0
     for _ in range(args.steps):
-        t, nnz, kind = cpu_spmv_time(dtype, m, rows, threads, 1)
+        t, nnz, kind, _ = cpu_spmv_time(dtype, m, rows, threads, 1)
         times.append(t)
     ms = 1e3 * float(np.mean(times))
     value = 2.0 * nnz / (ms * 1e-3) / 1e9
@@ -449,12 +449,21 @@ def run_ours(args):
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         probe = min(n_local, 100_000)
-        t_probe, nnz_probe, kind = cpu_spmv_time(dtype, m, probe, 1, 1)
+        t_probe, nnz_probe, kind, _ = cpu_spmv_time(dtype, m, probe, 1, 1)
         rows = int(min(n_local, max(probe, np.searchsorted(m["row_ptr"], nnz_probe / max(t_probe, 1e-9) * 4.0))))
-        t_cpu, nnz_cpu, kind = cpu_spmv_time(dtype, m, rows, 1, 3)
+        t_cpu, nnz_cpu, kind, y_cpu = cpu_spmv_time(dtype, m, rows, 1, 3)
         cpu = {"value": 2.0 * nnz_cpu / t_cpu / 1e9, "unit": UNIT, "cores": 1, "kind": kind,
                "sample": f"first {rows} of {n_local} rows ({nnz_cpu} nnz), serial, best of 3",
                "host_threads_available": cpu_threads()}
+        # the serial result doubles as the checker of the product that was just timed (same rows, same x)
+        import oracle
+
+        y_dev_rows = y_full[:rows].cpu().numpy() if dtype == mx.FP64 else y_full[:rows].cpu().view(torch.int16).numpy().view(np.float16)
+        rp_s = m["row_ptr"][: rows + 1]
+        err = oracle.y_error(dtype, y_dev_rows, y_cpu, rp_s, m["col_ind"], m["val"], m["x"])
+        tol = 1e-12 if dtype == mx.FP64 else 2e-3
+        cpu["parity"] = {"rows_checked": rows, "max_err_over_max_abs_rowsum": float(err), "tolerance": tol,
+                         "ok": bool(err <= tol)}
         if st.active and m["nnz"] <= 60_000_000:
             # the host extraction the device pipeline replaces, restated on the CPU (oracle), one run
             import oracle
