@@ -289,6 +289,12 @@ def run_ours(args):
             with torch.cuda.stream(stream):
                 peer_y.finish()
             last_y[0] = buf
+        elif peer_y is not None and method[0] == "multicast":
+            buf, ptrs = peer_y.next()
+            h.spmv_multicast(x_dev, ptrs, peer_y.multicast_ptr, rank * n_local)
+            with torch.cuda.stream(stream):
+                peer_y.finish()
+            last_y[0] = buf
         elif peer_y is not None and method[0] == "push":
             buf, ptrs = peer_y.next()
             h.spmv(x_dev, buf[rank * n_local: (rank + 1) * n_local])
@@ -347,7 +353,7 @@ def run_ours(args):
     if world > 1 and peer_y is not None and args.gather == "auto":
         # pick the fastest way of assembling y for this workload (all ranks agree: the times are max-reduced)
         trial = {}
-        for mth in ("epilogue", "push", "nccl"):
+        for mth in ("epilogue", "multicast", "push", "nccl") if peer_y.mc_ptrs[0] else ("epilogue", "push", "nccl"):
             saved = peer_y
             if mth == "nccl":
                 peer_y = None
@@ -361,8 +367,9 @@ def run_ours(args):
             gather = "nccl all-gather"
         else:
             method[0] = best
-            gather = ("fused into the SpMV epilogue (peer stores over NVLink + barrier)" if best == "epilogue"
-                      else "peer push kernel (16-byte stores over NVLink + barrier)")
+            gather = {"epilogue": "fused into the SpMV epilogue (peer stores over NVLink + barrier)",
+                      "multicast": "fused into the SpMV epilogue (multimem stores through NVSwitch multicast + barrier)",
+                      "push": "peer push kernel (16-byte stores over NVLink + barrier)"}[best]
         gather += " [auto: " + ", ".join(f"{k} {v * 1e3:.0f} us" for k, v in trial.items()) + "]"
     ms_step = timed(step_device, args.steps, max(3, args.warmup))
     value = 2.0 * nnz_total / (ms_step * 1e-3) / 1e9

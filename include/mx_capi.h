@@ -122,6 +122,13 @@ int mx_spmv(mx_handle_t h, const void *x_dev, void *y_dev);
  * computing.  The caller runs a barrier across the GPUs afterwards (every y is complete once all GPUs have passed it);
  * nothing in the kernels waits on another GPU. */
 int mx_spmv_peers(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, long long row_offset);
+/* mx_spmv_peers with the rows sent through NVSwitch multicast: y_multicast is the multicast address of the same
+ * buffers (every GPU's y bound to one NVLink multicast object, e.g. torch symmetric memory's multicast_ptr).  Each
+ * 8-byte row - or aligned pair of adjacent 2-byte rows - leaves the GPU as ONE multimem.st that the switch writes
+ * into every GPU's copy; rows that cannot be paired fall back to the peer stores of mx_spmv_peers.  Same barrier
+ * obligation afterwards.  No counterpart in the reference. */
+int mx_spmv_multicast(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, void *y_multicast,
+                      long long row_offset);
 /* The unfused alternative for small slabs: after mx_spmv wrote this GPU's rows into its own full-length y
  * (y_peers[self] + row_offset), copy those rows into the same place of every other GPU's y with 16-byte peer stores.
  * table_dev: 64 bytes of device memory the call may use (the peers' row addresses).  Followed, like mx_spmv_peers, by

@@ -83,6 +83,7 @@ SYMBOLS = {
     "mx_spmv": (_i, [_vp, _vp, _vp]),
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
+    "mx_spmv_multicast": (_i, [_vp, _vp, C.POINTER(_vp), _i, _vp, C.c_longlong]),
     "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
     "mx_read_matrix_market": (_i, [C.c_char_p, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
                                    C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
@@ -238,6 +239,16 @@ class MatXtract:
         if arr is None:
             arr = self._peer_arrays[key] = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
         self._ck(lib().mx_spmv_peers(self._h, _ptr(x_dev), arr, len(peer_ptrs), int(row_offset)))
+
+    def spmv_multicast(self, x_dev, peer_ptrs, multicast_ptr: int, row_offset: int):
+        """As spmv_peers, with the rows leaving through the buffers' NVLink multicast address (one store per row or
+        row pair, replicated by the switch)."""
+        key = tuple(peer_ptrs)
+        arr = self._peer_arrays.get(key)
+        if arr is None:
+            arr = self._peer_arrays[key] = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        self._ck(lib().mx_spmv_multicast(self._h, _ptr(x_dev), arr, len(peer_ptrs), C.c_void_p(int(multicast_ptr)),
+                                         int(row_offset)))
 
     def peer_push(self, peer_ptrs, self_rank: int, row_offset: int, n_rows: int, table_dev):
         """Copies this GPU's rows of y (already in its own full-length buffer) to every other GPU's buffer."""

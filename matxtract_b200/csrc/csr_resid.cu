@@ -103,7 +103,36 @@ struct RowOut {
     V *peer_y[MAX_PEERS];                  // OUT_Y_PEERS: every GPU's full-length y (peer-mapped), this GPU's included
     int n_peers;
     long long row_offset;                  // OUT_Y_PEERS: first row of this GPU's slab in the full y
+    V *mc_y;                               // OUT_Y_PEERS: the same y through its NVLink multicast address (or null):
+                                           // one store, replicated into every GPU's copy by the switch
 };
+
+// one store to a multicast address: the switch writes it into every GPU's copy of the buffer
+__device__ __forceinline__ void multicast_store64(double *mc, double v) {
+    asm volatile("multimem.st.relaxed.sys.global.f64 [%0], %1;" ::"l"(mc), "d"(v) : "memory");
+}
+__device__ __forceinline__ void multicast_store32(void *mc, unsigned v) {
+    asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
+// the row's final value: its sum plus what the tile half and (when accumulating) the old y contribute
+template <typename V, bool HAS_TILE, int MODE>
+__device__ __forceinline__ typename AccOf<V>::T row_value(const RowOut<V> &o, int r, typename AccOf<V>::T v) {
+    if (HAS_TILE) {
+        if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
+    }
+    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
+    return v;
+}
+
+// plain stores into every GPU's y over NVLink: consecutive rows of a warp make contiguous segments, and the traffic
+// overlaps the rest of the kernel (which is bound by x gathers, not by NVLink)
+template <typename V>
+__device__ __forceinline__ void store_peers(const RowOut<V> &o, int r, typename AccOf<V>::T v) {
+#pragma unroll
+    for (int g = 0; g < MAX_PEERS; ++g)
+        if (g < o.n_peers) from_acc(v, o.peer_y[g] + o.row_offset + r);
+}
 
 template <typename V, bool HAS_TILE, int MODE>
 __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename AccOf<V>::T v) {
@@ -111,19 +140,34 @@ __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename Ac
         o.carrier_out[o.row_map[r]] = v;
         return;
     }
-    if (HAS_TILE) {
-        if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
-    }
-    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
+    v = row_value<V, HAS_TILE, MODE>(o, r, v);
     if (MODE == OUT_Y_PEERS) {
-        // plain stores into every GPU's y over NVLink: consecutive rows of a warp make contiguous segments, and the
-        // traffic overlaps the rest of the kernel (which is bound by x gathers, not by NVLink)
-#pragma unroll
-        for (int g = 0; g < MAX_PEERS; ++g)
-            if (g < o.n_peers) from_acc(v, o.peer_y[g] + o.row_offset + r);
+        if constexpr (sizeof(V) == 8) {
+            if (o.mc_y) {
+                multicast_store64(reinterpret_cast<double *>(o.mc_y) + o.row_offset + r, v);
+                return;
+            }
+        }
+        store_peers<V>(o, r, v);  // 2-byte rows cannot be multicast one by one: see store_rows_multicast16
         return;
     }
     from_acc(v, o.y + r);
+}
+
+// FP16 rows through the multicast address, called by all 32 lanes of a warp (valid: this lane has a row).  The
+// smallest multicast store is 4 bytes, so a lane whose row starts an aligned pair and whose right neighbour holds the
+// next row stores both; rows left single go to every GPU with plain 2-byte stores.
+__device__ __forceinline__ void store_rows_multicast16(const RowOut<__half> &o, bool valid, int r, float v, int lane) {
+    const unsigned h = (unsigned)__half_as_ushort(__float2half_rn(v));
+    const unsigned hn = __shfl_down_sync(0xffffffffu, h, 1);
+    const int rn = __shfl_down_sync(0xffffffffu, r, 1);
+    const bool vn = __shfl_down_sync(0xffffffffu, (int)valid, 1) != 0;
+    const bool pack = valid && vn && lane < 31 && rn == r + 1 && (((o.row_offset + r) & 1LL) == 0);
+    const bool taken = __shfl_up_sync(0xffffffffu, (int)pack, 1) != 0 && lane > 0;
+    if (pack)
+        multicast_store32(o.mc_y + o.row_offset + r, h | (hn << 16));
+    else if (valid && !taken)
+        store_peers<__half>(o, r, v);
 }
 
 // read-only loads that do not displace the gathered x from L1 (L2 evict-first / evict-last cache-policy hints on the
@@ -345,6 +389,22 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
 
     // ---- coalesced epilogue: one row per thread per pass ----
     if (headOpen && nEmit > 0 && tid == 0) head[t] = ysum[0];  // the fix-up kernel finishes rows that span tiles
+    if constexpr (MODE == OUT_Y_PEERS && sizeof(V) == 2) {
+        if (out.mc_y) {  // warp-uniform loop: the lanes of a warp pair up their rows
+            for (int qb = headOpen ? 1 : 0; qb < nEmit; qb += THREADS) {
+                const int q = qb + tid;
+                const bool valid = q < nEmit;
+                int r = 0;
+                A v = A(0);
+                if (valid) {
+                    r = q == q0 ? rz : (out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q);
+                    v = row_value<V, HAS_TILE, MODE>(out, r, ysum[q]);
+                }
+                store_rows_multicast16(out, valid, r, v, lane);
+            }
+            return;
+        }
+    }
     if (q0 < nEmit) store_row<V, HAS_TILE, MODE>(out, rz, ysum[q0]);
     for (int q = q0 + THREADS; q < nEmit; q += THREADS) {
         const int r = out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q;
@@ -406,7 +466,7 @@ __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ p
 template <typename V>
 cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void *ytile, const uint32_t *hotmask,
                          int mode, const int *row_map, cudaStream_t s, bool chained, void *const *peers = nullptr,
-                         int n_peers = 0, long long row_offset = 0) {
+                         int n_peers = 0, long long row_offset = 0, void *mc_y = nullptr) {
     using A = typename AccOf<V>::T;
     constexpr int IPT = ResidCfg<V>::IPT;
     const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
@@ -419,6 +479,7 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     out.nzRow = P.nz_row;
     out.n_peers = n_peers;
     out.row_offset = row_offset;
+    out.mc_y = (V *)mc_y;
     for (int g = 0; g < MAX_PEERS; ++g) out.peer_y[g] = g < n_peers ? (V *)peers[g] : nullptr;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
@@ -538,13 +599,13 @@ cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, co
 
 cudaError_t resid_spmv_peers(int dtype, const ResidPlan &P, const void *x, void *const *peers, int n_peers,
                              long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
-                             bool chained) {
+                             bool chained, void *mc_y) {
     if (n_peers < 1 || n_peers > MAX_PEERS) return cudaErrorInvalidValue;
     if (dtype == MX_FP64)
         return resid_spmv_t<double>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, chained, peers, n_peers,
-                                    row_offset);
+                                    row_offset, mc_y);
     return resid_spmv_t<__half>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, chained, peers, n_peers,
-                                row_offset);
+                                row_offset, mc_y);
 }
 
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, void *carrier, const int *row_map,

@@ -1,5 +1,6 @@
 // C ABI of libmatxtract_b200.so: handle management, matrix upload, extraction, SpMV, timing loops, and the
 // stateless mirrors of the reference's host API (include/MatXtract.h).  See include/mx_capi.h.
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -241,7 +242,8 @@ static cudaError_t dd_enqueue(mx_handle_t h, const void *x) {
 }
 
 static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid,
-                        bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0) {
+                        bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0,
+                        void *mc_y = nullptr) {
     if (peers) {  // final rows go to every GPU's y
         const void *x = x_dev;
         if (h->stats.active) {
@@ -253,7 +255,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         }
         HCK(resid_spmv_peers(h->dtype, h->resid, x, peers, n_peers, row_offset, h->stats.active ? h->ytile : nullptr,
                              h->stats.active ? h->part.hotmask : nullptr, h->stream,
-                             h->stats.active != 0 && !h->dd_use_tile));
+                             h->stats.active != 0 && !h->dd_use_tile, mc_y));
         return MX_OK;
     }
     if (h->stats.active) {
@@ -680,6 +682,17 @@ int mx_spmv_peers(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_peers: call mx_partition first");
     HCK(cudaSetDevice(h->device));
     return spmv_enqueue(h, x_dev, nullptr, true, true, true, y_peers, n_peers, row_offset);
+}
+
+int mx_spmv_multicast(mx_handle_t h, const void *x_dev, void *const *y_peers, int n_peers, void *y_multicast,
+                      long long row_offset) {
+    if (!h || !x_dev || !y_peers || !y_multicast || n_peers < 1 || n_peers > 8 || row_offset < 0) return MX_ERR_INVALID;
+    for (int g = 0; g < n_peers; ++g)
+        if (!y_peers[g]) return MX_ERR_INVALID;
+    if (((uintptr_t)y_multicast & 7u) != 0) return h->fail(MX_ERR_INVALID, "mx_spmv_multicast: address not 8-byte aligned");
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_multicast: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    return spmv_enqueue(h, x_dev, nullptr, true, true, true, y_peers, n_peers, row_offset, y_multicast);
 }
 
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {

@@ -123,10 +123,11 @@ cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y,
 // carrier[row_map[r]] = sum_r in the accumulate type: runs the core-dense block as CSR (low-fill dispatch)
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &plan, const void *x, void *carrier, const int *row_map,
                                   cudaStream_t s);
-// y_peer[g][row_offset + r] = row r for every g < n_peers (peer-mapped full-length y of every GPU): fused all-gather
+// y_peer[g][row_offset + r] = row r for every g < n_peers (peer-mapped full-length y of every GPU): fused all-gather.
+// mc_y (optional): the NVLink multicast address of the same buffers; rows then go out as one multicast store each.
 cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, void *const *peers, int n_peers,
                              long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
-                             bool chained = false);
+                             bool chained = false, void *mc_y = nullptr);
 int resid_launches(const ResidPlan &plan);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);

@@ -69,12 +69,19 @@ class PeerY:
             self.bufs.append(t)
             self.hdls.append(symm_mem.rendezvous(t, group))
         self.ptrs = [list(h.buffer_ptrs) for h in self.hdls]
+        # NVLink multicast address of each buffer (0 when the box has no multicast support)
+        self.mc_ptrs = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.hdls]
         self.k = 0
 
     def next(self):
         """(tensor that will hold the next product, device addresses of that buffer on every GPU)."""
         self.k ^= 1
         return self.bufs[self.k], self.ptrs[self.k]
+
+    @property
+    def multicast_ptr(self) -> int:
+        """Multicast address of the buffer next() returned last (0: not available)."""
+        return self.mc_ptrs[self.k]
 
     def finish(self):
         """Barrier across the GPUs on the current stream: afterwards the buffer returned by next() is complete."""
@@ -113,7 +120,8 @@ class DistributedSpMV:
             self._y = torch.zeros(max(self.rows, 1), dtype=tdt, device=self.device)[: self.rows]
             # fused: the kernels store y rows straight into every GPU's y (peer-mapped), one barrier afterwards
             self.peer_y = PeerY(n, tdt, self.device, group) if fused else None
-            self.fused = fused  # False (NCCL all-gather), True / "epilogue" (kernels store to all peers), "push"
+            # False (NCCL all-gather), True / "epilogue" (kernels store to all peers), "multicast", "push"
+            self.fused = fused
             self._table = torch.zeros(8, dtype=torch.int64, device=self.device)
         else:
             self._slab = (rp, ci, v)
@@ -131,6 +139,10 @@ class DistributedSpMV:
             if self.fused == "push":  # product into this GPU's own y, then 16-byte peer stores of the slab
                 self.handle.spmv(x_full, y[r0: r0 + self.rows])
                 self.handle.peer_push(ptrs, self.rank, r0, self.rows, self._table)
+            elif self.fused == "multicast":  # rows leave through the NVLink multicast address of the buffers
+                if not self.peer_y.multicast_ptr:
+                    raise RuntimeError("symmetric memory has no multicast address on this box")
+                self.handle.spmv_multicast(x_full, ptrs, self.peer_y.multicast_ptr, r0)
             else:
                 self.handle.spmv_peers(x_full, ptrs, r0)
             with torch.cuda.stream(self.stream):
