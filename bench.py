@@ -353,7 +353,9 @@ def run_ours(args):
     if world > 1 and peer_y is not None and args.gather == "auto":
         # pick the fastest way of assembling y for this workload (all ranks agree: the times are max-reduced)
         trial = {}
-        for mth in ("epilogue", "multicast", "push", "nccl") if peer_y.mc_ptrs[0] else ("epilogue", "push", "nccl"):
+        # multicast stores measured slower than the plain peer stores (2-byte rows, 8 GPUs): timed only on request
+        want_mc = peer_y.mc_ptrs[0] and os.environ.get("MX_BENCH_MULTICAST", "0") == "1"
+        for mth in ("epilogue", "multicast", "push", "nccl") if want_mc else ("epilogue", "push", "nccl"):
             saved = peer_y
             if mth == "nccl":
                 peer_y = None

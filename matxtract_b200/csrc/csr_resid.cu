@@ -103,8 +103,10 @@ struct RowOut {
     V *peer_y[MAX_PEERS];                  // OUT_Y_PEERS: every GPU's full-length y (peer-mapped), this GPU's included
     int n_peers;
     long long row_offset;                  // OUT_Y_PEERS: first row of this GPU's slab in the full y
-    V *mc_y;                               // OUT_Y_PEERS: the same y through its NVLink multicast address (or null):
-                                           // one store, replicated into every GPU's copy by the switch
+    // OUT_Y_PEERS with multicast stores: carrier_out (unused in that mode) carries the NVLink multicast address of
+    // the same y buffers, or null.  A member of its own changed the register allocation of every variant of the
+    // kernel (all up to the launch-bound cap) and cost 4 % on the single-GPU product.
+    __device__ __forceinline__ V *multicast() const { return reinterpret_cast<V *>(carrier_out); }
 };
 
 // one store to a multicast address: the switch writes it into every GPU's copy of the buffer
@@ -140,11 +142,14 @@ __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename Ac
         o.carrier_out[o.row_map[r]] = v;
         return;
     }
-    v = row_value<V, HAS_TILE, MODE>(o, r, v);
+    if (HAS_TILE) {
+        if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
+    }
+    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
     if (MODE == OUT_Y_PEERS) {
         if constexpr (sizeof(V) == 8) {
-            if (o.mc_y) {
-                multicast_store64(reinterpret_cast<double *>(o.mc_y) + o.row_offset + r, v);
+            if (o.multicast()) {
+                multicast_store64(reinterpret_cast<double *>(o.multicast()) + o.row_offset + r, v);
                 return;
             }
         }
@@ -165,7 +170,7 @@ __device__ __forceinline__ void store_rows_multicast16(const RowOut<__half> &o, 
     const bool pack = valid && vn && lane < 31 && rn == r + 1 && (((o.row_offset + r) & 1LL) == 0);
     const bool taken = __shfl_up_sync(0xffffffffu, (int)pack, 1) != 0 && lane > 0;
     if (pack)
-        multicast_store32(o.mc_y + o.row_offset + r, h | (hn << 16));
+        multicast_store32(o.multicast() + o.row_offset + r, h | (hn << 16));
     else if (valid && !taken)
         store_peers<__half>(o, r, v);
 }
@@ -390,7 +395,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     // ---- coalesced epilogue: one row per thread per pass ----
     if (headOpen && nEmit > 0 && tid == 0) head[t] = ysum[0];  // the fix-up kernel finishes rows that span tiles
     if constexpr (MODE == OUT_Y_PEERS && sizeof(V) == 2) {
-        if (out.mc_y) {  // warp-uniform loop: the lanes of a warp pair up their rows
+        if (out.multicast()) {  // warp-uniform loop: the lanes of a warp pair up their rows
             for (int qb = headOpen ? 1 : 0; qb < nEmit; qb += THREADS) {
                 const int q = qb + tid;
                 const bool valid = q < nEmit;
@@ -472,14 +477,13 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
     RowOut<V> out;
     out.y = (V *)y;
-    out.carrier_out = (A *)y;
+    out.carrier_out = mode == OUT_Y_PEERS ? (A *)mc_y : (A *)y;
     out.row_map = row_map;
     out.ytile = (const A *)ytile;
     out.hotmask = hotmask;
     out.nzRow = P.nz_row;
     out.n_peers = n_peers;
     out.row_offset = row_offset;
-    out.mc_y = (V *)mc_y;
     for (int g = 0; g < MAX_PEERS; ++g) out.peer_y[g] = g < n_peers ? (V *)peers[g] : nullptr;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
