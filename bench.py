@@ -378,6 +378,44 @@ def run_ours(args):
     ms_e2e = timed(step_e2e, max(10, args.steps // 10), 3)
     e2e_value = 2.0 * nnz_total / (ms_e2e * 1e-3) / 1e9
 
+    # N > 1: where a step's time goes on every rank - this rank's kernels, then the wait for the others (barrier or
+    # collective) - from events recorded inside a separate, untimed run of the same steps
+    exchange = None
+    if world > 1:
+        k = min(200, max(20, args.steps // 2))
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(k)]
+        barrier()
+        for i in range(k):
+            ev[i][0].record(stream)
+            if peer_y is not None:
+                buf, ptrs = peer_y.next()
+                if method[0] == "push":
+                    h.spmv(x_dev, buf[rank * n_local: (rank + 1) * n_local])
+                    h.peer_push(ptrs, rank, rank * n_local, n_local, push_table)
+                elif method[0] == "multicast":
+                    h.spmv_multicast(x_dev, ptrs, peer_y.multicast_ptr, rank * n_local)
+                else:
+                    h.spmv_peers(x_dev, ptrs, rank * n_local)
+                ev[i][1].record(stream)
+                with torch.cuda.stream(stream):
+                    peer_y.finish()
+            else:
+                h.spmv(x_dev, y_work)
+                ev[i][1].record(stream)
+                with torch.cuda.stream(stream):
+                    dist.all_gather_into_tensor(y_full, y_work)
+            ev[i][2].record(stream)
+        barrier()
+        own = sum(e[0].elapsed_time(e[1]) for e in ev) / k
+        wait = sum(e[1].elapsed_time(e[2]) for e in ev) / k
+        t = torch.tensor([own, wait], device=f"cuda:{local}", dtype=torch.float64)
+        allt = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        exchange = {"steps": k, "own_kernels_ms_per_rank": [round(float(a[0]), 4) for a in allt],
+                    "wait_for_others_ms_per_rank": [round(float(a[1]), 4) for a in allt],
+                    "note": "own = this rank's launches of one step (rows stored to the peers included when fused); "
+                            "wait = barrier or collective until every rank's rows have arrived"}
+
     # per-kernel timing (each half alone, CUDA events on the handle's stream) for the roofline of the dominant kernel
     sampler.active.set()
     halves = h.spmv_timed(x_dev, y_work, warm=max(3, args.warmup), iters=args.steps)
@@ -509,6 +547,8 @@ def run_ours(args):
         "gpu_launches": h.launches_per_spmv * args.steps,
         "clocks": sampler.summary(),
     }
+    if exchange is not None:
+        line["exchange"] = exchange
     if cusparse is not None:
         line["library_baseline"] = cusparse
     if cpu is not None:
