@@ -11,7 +11,8 @@ scaling.  Prints one JSON line (rank 0).  Beside the contract's keys it carries,
 the same run: "library_baseline" (cuSPARSE's CSR SpMV on the same matrix and x, through torch.mv) and
 "roofline.stream_gather_floor_ms" (a pass over the same CSR that streams indices and values and gathers x but has no
 row logic and writes nothing: what the matrix's index pattern allows a CSR-ordered kernel on this GPU), and
-"csr_l2_prefetch_tiles" (what the plan-time tuner chose for the CSR kernels).
+"csr_l2_prefetch_tiles" (what the plan-time tuner chose for the CSR kernels).  At N > 1 it carries "exchange": for every
+rank, the mean time of its own launches of a step and the mean time it then waits for the other ranks' rows.
 
 --impl reference times the reference's serial CPU SpMV (its spmv_serial, from oracle/_ref when that was built from the
 reference sources, else the oracle port) on all host cores over row slabs of a bounded sample of the same workload.
