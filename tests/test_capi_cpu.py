@@ -96,3 +96,19 @@ def test_algorithmic_bytes_formula():
     # reference test/test_cdspmv.cpp:214: (nnz + cols + rows)*sizeof(val) + nnz*4 + (rows+1)*4
     assert synth.algorithmic_bytes(10, 10, 100, mx.FP64) == (100 + 10 + 10) * 8 + 100 * 4 + 11 * 4
     assert synth.algorithmic_bytes(10, 10, 100, mx.FP16) == (100 + 10 + 10) * 2 + 100 * 4 + 11 * 4
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: include/mx_capi.h must compile as C99 on its own, and its two plain structs must have
+    the layout the ctypes mirror assumes."""
+    import subprocess
+
+    src = tmp_path / "t.c"
+    src.write_text('#include "mx_capi.h"\n#include <stdio.h>\nint main(void){printf("%zu %zu %zu\\n", '
+                   "sizeof(mx_partition_stats), sizeof(mx_dist_features), sizeof(mx_matrix_features)); return 0;}\n")
+    exe = tmp_path / "t"
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{ROOT / 'include'}",
+                        str(src), "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    sizes = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True).stdout.split()]
+    assert sizes == [C.sizeof(capi.PartitionStats), C.sizeof(capi.DistFeatures), C.sizeof(capi.MatrixFeatures)]
