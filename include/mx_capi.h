@@ -47,7 +47,10 @@ void *mx_stream(mx_handle_t h);
 int mx_sync(mx_handle_t h);
 
 /* Uploads a host CSR matrix (replaces the per-call cudaMalloc + cudaMemcpy of every reference wrapper,
- * e.g. src/spmv_kernel/cdSpMV.cu:407-418).  Any previous matrix and partition of the handle is dropped. */
+ * e.g. src/spmv_kernel/cdSpMV.cu:407-418).  Any previous matrix and partition of the handle is dropped.  The reference
+ * trusts its inputs (unchecked copies, include/common.h:81-90); here one pass on the device checks that row_ptr never
+ * decreases and that every column index lies in [0, n_cols) before any kernel uses them as addresses: a matrix that
+ * fails is refused with MX_ERR_INVALID and the handle is left without a matrix. */
 int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind,
                   const void *val);
 
@@ -72,6 +75,11 @@ typedef struct {
  * row-partitioned matrix) is accepted as well and is extracted on its own. */
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats);
 int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats);
+/* The int32 limit of the fragment format (the reference's indT, include/common.h:79, indexes both the fragments and
+ * the fragK x-index slots of each, test/test_autotc_spmv.cpp:1384-1404): MX_OK when `total_frags` fragments can be
+ * indexed, MX_ERR_OVERFLOW when not.  mx_partition applies this rule to the fragment total (taken in 64 bits on the
+ * device) and fails with MX_ERR_OVERFLOW instead of wrapping.  Host-only. */
+int mx_fragment_count_status(long long total_frags, int dtype);
 /* Shape of the matrix the handle holds (uploaded, or restored by mx_load_partition). */
 int mx_dims(mx_handle_t h, int *n_rows, int *n_cols, int *nnz);
 
@@ -81,7 +89,13 @@ int mx_dims(mx_handle_t h, int *n_rows, int *n_cols, int *nnz);
  * needs no uploaded matrix (and drops one that is there), builds the execution plans and leaves the handle ready for
  * mx_spmv.  A loaded handle cannot be re-extracted with other taus (the original CSR is not in the file). */
 int mx_save_partition(mx_handle_t h, const char *path);
+/* Every array of the file ends up as addresses in the kernels, so the whole file is read and checked on the host
+ * before anything is uploaded (pointer arrays monotone and ending at their counts, row ids distinct and in range,
+ * xperm a permutation, column ids in range, value counts equal to the bitmaps' population counts); a file that fails
+ * is refused with MX_ERR_INVALID and the handle is left empty. */
 int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats);
+/* The loader's check alone, without a GPU: MX_OK, or MX_ERR_INVALID with what is wrong in msg (if msg != NULL). */
+int mx_check_partition_file(const char *path, int dtype, char *msg, int msg_len);
 
 /* Searches (tau_c, tau_r) on the device instead of the reference's 20-run Bayesian search through the command-line
  * driver (ML/bayes_opt.py:153-163): every valid point of the grid {0, 1/grid, ..., (grid-1)/grid}^2 with
@@ -231,29 +245,6 @@ int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int 
 #define MX_STATIC_SCRATCH_BYTES (24u << 20)
 int mx_csr_spmv_static(int dtype, int n_rows, int n_cols, int nnz, const int *row_ptr_dev, const int *col_ind_dev,
                        const void *val_dev, const void *x_dev, void *y_dev, void *stream);
-
-/* ---- synthetic inputs (host code) ----------------------------------------------------------------- */
-enum { MX_SYNTH_UNIFORM = 0, MX_SYNTH_POWERLAW = 1, MX_SYNTH_BLOCK = 2, MX_SYNTH_HOTCOL = 3 };
-typedef struct {
-    int kind;
-    int64_t n;            /* square dimension */
-    uint64_t seed;
-    double mean_len;      /* UNIFORM: Poisson mean; HOTCOL: mean row length (1 + geometric) */
-    double zipf_s;        /* POWERLAW: exponent of the row-length law */
-    double alpha;         /* POWERLAW: length = clip(ceil(alpha * K), 1, max_len) */
-    int64_t max_len;      /* POWERLAW: clip */
-    double local_frac;    /* POWERLAW: share of a row's columns within +-local_halfwidth of the row index */
-    int64_t local_halfwidth; /* POWERLAW: columns; BLOCK: block columns */
-    int blocks_per_row;   /* BLOCK: dense 8x8 blocks per block row */
-    double hot_col_frac;  /* HOTCOL: share of columns that are hot */
-    double hot_nnz_frac;  /* HOTCOL: share of entries drawn from the hot columns */
-    int normal_values;    /* values ~ N(0,1) instead of U(-1,1) */
-} mx_synth_params;
-/* Row pointers (relative to row_begin) of rows [row_begin, row_end); row_ptr_out has row_end-row_begin+1 ints. */
-int mx_synth_row_lengths(const mx_synth_params *p, int64_t row_begin, int64_t row_end, int *row_ptr_out);
-int mx_synth_fill(const mx_synth_params *p, int dtype, int64_t row_begin, int64_t row_end, const int *row_ptr,
-                  int *col_ind, void *val);
-int mx_synth_vector(uint64_t seed, int dtype, int64_t begin, int64_t end, void *x);
 
 #ifdef __cplusplus
 }

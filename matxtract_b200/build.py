@@ -17,11 +17,24 @@ CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 OBJDIR = LIBDIR / "obj"
 LIB = LIBDIR / "libmatxtract_b200.so"
+SYNTH_LIB = LIBDIR / "libmx_synth.so"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fopenmp", "-ccbin", "/usr/bin/g++",
                      f"-I{ROOT / 'include'}", f"-I{CSRC}"]
+
+
+def source_hash() -> str:
+    """Short hash of the kernel sources and headers the library is built from (ties an ncu summary to a build)."""
+    import hashlib
+
+    hsh = hashlib.sha256()
+    files = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cpp")))
+    for f in files:
+        hsh.update(f.name.encode())
+        hsh.update(f.read_bytes())
+    return hsh.hexdigest()[:12]
 
 
 def _newer(src: Path, dst: Path, extra=()) -> bool:
@@ -89,10 +102,11 @@ def build_all(verbose: bool = False, force: bool = False, ptxas_info: bool = Fal
             _run(["/usr/bin/g++", "-std=c++17", "-O2", f"-I{ROOT / 'include'}", feat, f"-L{LIBDIR}", "-lmatxtract_b200",
                   "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64",
                   "-o", exe], verbose)
-    probe = CSRC / "probe" / "gather_ceiling.cu"
-    exe = LIBDIR / "gather_ceiling"
-    if probe.exists() and (force or _newer(probe, exe)):
-        _run([NVCC, *ARCH, "-O3", "-ccbin", "/usr/bin/g++", probe, "-o", exe], verbose)
+    # the synthetic-input generator: host code in a library of its own (include/mx_synth.h)
+    synth = CSRC / "synth" / "synth.cpp"
+    if force or _newer(synth, SYNTH_LIB, [ROOT / "include" / "mx_synth.h"]):
+        _run(["/usr/bin/g++", "-std=c++17", "-O2", "-fPIC", "-fopenmp", "-shared", f"-I{ROOT / 'include'}",
+              "-I/usr/local/cuda/include", synth, "-o", SYNTH_LIB], verbose)
     return LIB
 
 

@@ -9,10 +9,8 @@ import numpy as np
 FP64, FP16 = 0, 1
 DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
 COLSPACE_AUTO, COLSPACE_PERMUTED, COLSPACE_ORIGINAL = 0, 1, 2
-import os
 
-# MATXTRACT_B200_LIB points at another build of the same library (e.g. one compiled with different tile constants)
-_LIB_PATH = Path(os.environ.get("MATXTRACT_B200_LIB", Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"))
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
 
 STATUS = {0: "MX_OK", 1: "MX_ERR_INVALID", 2: "MX_ERR_CUDA", 3: "MX_ERR_TAU", 4: "MX_ERR_STATE", 5: "MX_ERR_OVERFLOW",
           6: "MX_ERR_TIMEOUT", 7: "MX_ERR_NOMEM", 8: "MX_ERR_NO_DEVICE", 9: "MX_ERR_TOO_LARGE"}
@@ -54,13 +52,6 @@ class _PartitionArrays(C.Structure):
                                            "fragPtr", "fragBit", "tcVal", "rowPtr_CD", "colInd_CD", "val_CD")]
 
 
-class SynthParams(C.Structure):
-    _fields_ = [("kind", C.c_int), ("n", C.c_int64), ("seed", C.c_uint64), ("mean_len", C.c_double),
-                ("zipf_s", C.c_double), ("alpha", C.c_double), ("max_len", C.c_int64), ("local_frac", C.c_double),
-                ("local_halfwidth", C.c_int64), ("blocks_per_row", C.c_int), ("hot_col_frac", C.c_double),
-                ("hot_nnz_frac", C.c_double), ("normal_values", C.c_int)]
-
-
 # every symbol include/mx_capi.h declares: name -> (restype, argtypes)
 _vp, _i, _d = C.c_void_p, C.c_int, C.c_double
 _ip = C.POINTER(C.c_int)
@@ -77,7 +68,9 @@ SYMBOLS = {
     "mx_partition_stats_get": (_i, [_vp, C.POINTER(PartitionStats)]),
     "mx_save_partition": (_i, [_vp, C.c_char_p]),
     "mx_load_partition": (_i, [_vp, C.c_char_p, C.POINTER(PartitionStats)]),
+    "mx_check_partition_file": (_i, [C.c_char_p, _i, C.c_char_p, _i]),
     "mx_autotune_tau": (_i, [_vp, _i, C.POINTER(_d), C.POINTER(_d), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mx_fragment_count_status": (_i, [C.c_longlong, _i]),
     "mx_dims": (_i, [_vp, _ip, _ip, _ip]),
     "mx_download_partition": (_i, [_vp, C.POINTER(_PartitionArrays)]),
     "mx_spmv": (_i, [_vp, _vp, _vp]),
@@ -103,9 +96,6 @@ SYMBOLS = {
     "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
     "mx_se_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d)]),
     "mx_csr_spmv_static": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "mx_synth_row_lengths": (_i, [C.POINTER(SynthParams), C.c_int64, C.c_int64, _vp]),
-    "mx_synth_fill": (_i, [C.POINTER(SynthParams), _i, C.c_int64, C.c_int64, _vp, _vp, _vp]),
-    "mx_synth_vector": (_i, [C.c_uint64, _i, C.c_int64, C.c_int64, _vp]),
 }
 
 _lib = None
@@ -259,8 +249,11 @@ class MatXtract:
         _raise(lib().mx_peer_push(self.dtype, arr, len(peer_ptrs), self_rank, int(row_offset), int(n_rows),
                                   _ptr(table_dev), C.c_void_p(self.stream)))
 
-    def spmv_host(self, x: np.ndarray, y: np.ndarray | None = None) -> np.ndarray:
-        x = _c(x, np_dtype(self.dtype))
+    def spmv_host(self, x, y=None):
+        """y = A x with HOST buffers (numpy arrays, or pinned torch CPU tensors of the handle's value type): copies x
+        in, multiplies, copies y out, synchronises."""
+        if isinstance(x, np.ndarray):
+            x = _c(x, np_dtype(self.dtype))
         if y is None:
             y = np.empty(self.n_rows, np_dtype(self.dtype))
         self._ck(lib().mx_spmv_host(self._h, _ptr(x), _ptr(y)))
@@ -330,6 +323,13 @@ class MatXtract:
 def _raise(st):
     if st != 0:
         raise MxError(st, lib().mx_status_string(st).decode())
+
+
+def check_partition_file(path, dtype: int) -> str:
+    """'' when the stored partition at `path` passes the loader's host-side check, else what is wrong.  No GPU."""
+    msg = C.create_string_buffer(256)
+    lib().mx_check_partition_file(str(path).encode(), dtype, msg, 256)
+    return msg.value.decode()
 
 
 def read_matrix_market(path, dtype: int, threads: int = 0):

@@ -595,7 +595,7 @@ void resid_plan_free(ResidPlan &P, cudaStream_t s) {
 int resid_launches(const ResidPlan &P) { return (P.num_tiles > 1 || P.n_empty > 0) ? 2 : 1; }
 
 cudaError_t resid_spmv(int dtype, const ResidPlan &P, const void *x, void *y, const void *ytile,
-                       const uint32_t *hotmask, bool accumulate, int *, cudaStream_t s, bool chained) {
+                       const uint32_t *hotmask, bool accumulate, cudaStream_t s, bool chained) {
     const int mode = accumulate ? OUT_Y_ACCUM : OUT_Y;
     if (dtype == MX_FP64) return resid_spmv_t<double>(P, x, y, ytile, hotmask, mode, nullptr, s, chained);
     return resid_spmv_t<__half>(P, x, y, ytile, hotmask, mode, nullptr, s, chained);

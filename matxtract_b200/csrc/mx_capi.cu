@@ -7,6 +7,7 @@
 #include <string>
 
 #include "mx_internal.h"
+#include "partition_file.h"
 
 using namespace mx;
 
@@ -95,6 +96,7 @@ void drop_matrix(mx_handle_t h) {
     h->row_ptr = h->col_ind = nullptr;
     h->val = h->x_stage = h->y_stage = nullptr;
     h->has_matrix = false;
+    h->n_rows = h->n_cols = h->nnz = 0;
 }
 
 int check_device() {
@@ -218,7 +220,19 @@ int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row
         HCK(cudaMemcpyAsync(h->col_ind, col_ind, sizeof(int) * (size_t)nnz, cudaMemcpyHostToDevice, h->stream));
         HCK(cudaMemcpyAsync(h->val, val, vb * (size_t)nnz, cudaMemcpyHostToDevice, h->stream));
     }
+    // Every index of the matrix becomes an address in the kernels (x gathers, histogram bins, row segments), so one
+    // pass on the device checks them before anything dereferences one: row pointers non-decreasing, column ids in
+    // [0, n_cols).  A bad matrix is refused here and never reaches a kernel that would use it.
+    int bad = 0;
+    HCK(cudaMemsetAsync(h->dev_err, 0, sizeof(int), h->stream));
+    HCK(validate_csr(n_rows, n_cols, nnz, h->row_ptr, h->col_ind, h->dev_err, h->stream));
+    HCK(cudaMemcpyAsync(&bad, h->dev_err, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     HCK(cudaStreamSynchronize(h->stream));
+    if (bad) {
+        HCK(cudaMemsetAsync(h->dev_err, 0, sizeof(int), h->stream));
+        drop_matrix(h);
+        return h->fail(MX_ERR_INVALID, "mx_upload_csr: row_ptr decreases or a column index is outside [0, n_cols)");
+    }
     h->n_rows = n_rows;
     h->n_cols = n_cols;
     h->nnz = nnz;
@@ -266,10 +280,10 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         }
         if (do_tile) HCK(dd_enqueue(h, x));
         if (do_resid)
-            HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->dev_err, h->stream,
+            HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->stream,
                            /*chained=*/do_tile && !h->dd_use_tile));
     } else if (do_resid) {
-        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->dev_err, h->stream));
+        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
     }
     return MX_OK;
 }
@@ -444,30 +458,14 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
 }
 
 // ---- stored partitions ---------------------------------------------------------------------------------------
-namespace {
-const char kMagic[8] = {'M', 'X', 'P', 'A', 'R', 'T', '0', '1'};
-struct FileHeader {
-    char magic[8];
-    int32_t dtype, n_rows, n_cols, nnz;
-    int32_t dCols, nnzColD, sCols, nnzColS, dRows, nnzRowD, sRows, nnzRowS, chunkNum, totalFrags, nnzCD, fragK;
-    double tc_nnz_ratio;
-};
-struct FileCloser {
-    FILE *f;
-    ~FileCloser() {
-        if (f) fclose(f);
-    }
-};
-}  // namespace
-
 int mx_save_partition(mx_handle_t h, const char *path) {
     if (!h || !path) return MX_ERR_INVALID;
     if (!h->planned || !h->stats.active) return h->fail(MX_ERR_STATE, "mx_save_partition: no active partition");
     HCK(cudaSetDevice(h->device));
     const mx_partition_stats &s = h->stats;
-    const size_t vb = val_bytes(h->dtype), bb = bit_bytes(h->dtype);
-    FileHeader hd{};
-    memcpy(hd.magic, kMagic, 8);
+    PartFileHeader hd{};
+    memcpy(hd.magic, kPartMagic, 8);
+    hd.version = kPartVersion;
     hd.dtype = h->dtype;
     hd.n_rows = h->n_rows;
     hd.n_cols = h->n_cols;
@@ -476,32 +474,27 @@ int mx_save_partition(mx_handle_t h, const char *path) {
     hd.dRows = s.dRows, hd.nnzRowD = s.nnzRowD, hd.sRows = s.sRows, hd.nnzRowS = s.nnzRowS;
     hd.chunkNum = s.chunkNum, hd.totalFrags = s.totalFrags, hd.nnzCD = s.nnzCD, hd.fragK = s.fragK;
     hd.tc_nnz_ratio = s.tc_nnz_ratio;
-    FileCloser fc{fopen(path, "wb")};
+    struct FileCloser {
+        FILE *f;
+        ~FileCloser() {
+            if (f) fclose(f);
+        }
+    } fc{fopen(path, "wb")};
     if (!fc.f) return h->fail(MX_ERR_INVALID, std::string("cannot open for writing: ") + path);
     if (fwrite(&hd, sizeof hd, 1, fc.f) != 1) return h->fail(MX_ERR_INVALID, "write failed");
-    struct Arr {
-        const void *dev;
-        size_t bytes;
-    } arrs[] = {{h->part.xperm, sizeof(int) * (size_t)h->n_cols},
-                {h->part.rId, sizeof(int) * (size_t)s.dRows},
-                {h->part.rowPtr_dd, sizeof(int) * ((size_t)s.dRows + 1)},
-                {h->part.colInd_dd, sizeof(int) * (size_t)s.nnzRowD},
-                {h->part.val_dd, vb * (size_t)s.nnzRowD},
-                {h->part.tiles.chunkPtr, sizeof(int) * ((size_t)s.chunkNum + 1)},
-                {h->part.tiles.AToX, sizeof(int) * (size_t)s.totalFrags * s.fragK},
-                {h->part.tiles.fragPtr, sizeof(int) * ((size_t)s.totalFrags + 1)},
-                {h->part.tiles.fragBit, bb * (size_t)s.totalFrags},
-                {h->part.tiles.tcVal, vb * (size_t)s.nnzRowD},
-                {h->part.rowPtr_CD, sizeof(int) * ((size_t)h->n_rows + 1)},
-                {h->part.colInd_CD, sizeof(int) * (size_t)s.nnzCD},
-                {h->part.val_CD, vb * (size_t)s.nnzCD}};
+    uint64_t bytes[PA_COUNT];
+    part_array_bytes(hd, bytes);
+    const void *dev[PA_COUNT] = {h->part.xperm,          h->part.rId,         h->part.rowPtr_dd,     h->part.colInd_dd,
+                                 h->part.val_dd,         h->part.tiles.chunkPtr, h->part.tiles.AToX, h->part.tiles.fragPtr,
+                                 h->part.tiles.fragBit,  h->part.tiles.tcVal, h->part.rowPtr_CD,     h->part.colInd_CD,
+                                 h->part.val_CD};
     std::string buf;
-    for (const Arr &a : arrs) {
-        const uint64_t n = a.bytes;
+    for (int a = 0; a < PA_COUNT; ++a) {
+        const uint64_t n = bytes[a];
         if (fwrite(&n, sizeof n, 1, fc.f) != 1) return h->fail(MX_ERR_INVALID, "write failed");
         if (n == 0) continue;
         buf.resize(n);
-        HCK(cudaMemcpyAsync(&buf[0], a.dev, n, cudaMemcpyDeviceToHost, h->stream));
+        HCK(cudaMemcpyAsync(&buf[0], dev[a], n, cudaMemcpyDeviceToHost, h->stream));
         HCK(cudaStreamSynchronize(h->stream));
         if (fwrite(buf.data(), 1, n, fc.f) != n) return h->fail(MX_ERR_INVALID, "write failed");
     }
@@ -510,17 +503,20 @@ int mx_save_partition(mx_handle_t h, const char *path) {
 
 int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats) {
     if (!h || !path) return MX_ERR_INVALID;
-    FileCloser fc{fopen(path, "rb")};
-    if (!fc.f) return h->fail(MX_ERR_INVALID, std::string("cannot open: ") + path);
-    FileHeader hd{};
-    if (fread(&hd, sizeof hd, 1, fc.f) != 1 || memcmp(hd.magic, kMagic, 8) != 0)
-        return h->fail(MX_ERR_INVALID, "not a stored partition");
-    if (hd.dtype != h->dtype) return h->fail(MX_ERR_INVALID, "stored partition has the other value type");
-    if (hd.n_rows < 0 || hd.n_cols < 0 || hd.dRows < 0 || hd.nnzRowD < 0 || hd.nnzCD < 0 || hd.totalFrags < 0 ||
-        hd.fragK != frag_k(h->dtype))
-        return h->fail(MX_ERR_INVALID, "stored partition: bad header");
+    // the whole file is read and validated on the host before anything reaches the device: its arrays become
+    // addresses in the kernels
+    PartFile pf;
+    std::string problem = part_file_read(path, h->dtype, pf);
+    if (problem.empty()) problem = part_file_problem(pf);
+    if (!problem.empty()) return h->fail(MX_ERR_INVALID, "stored partition: " + problem);
+    const PartFileHeader &hd = pf.hd;
     HCK(cudaSetDevice(h->device));
     drop_matrix(h);  // a loaded partition replaces the matrix: it holds every entry (no re-extraction from it)
+    auto refuse = [&](int status) {  // nothing of a half-loaded partition stays behind
+        drop_matrix(h);
+        h->n_rows = h->n_cols = h->nnz = 0;
+        return status;
+    };
     h->n_rows = hd.n_rows;
     h->n_cols = hd.n_cols;
     h->nnz = hd.nnz;
@@ -531,50 +527,40 @@ int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats
     s.chunkNum = hd.chunkNum, s.totalFrags = hd.totalFrags, s.nnzCD = hd.nnzCD, s.fragK = hd.fragK;
     s.tc_nnz_ratio = hd.tc_nnz_ratio;
     s.active = 1;
-    const size_t vb = val_bytes(h->dtype), bb = bit_bytes(h->dtype);
-    struct Arr {
-        void **dev;
-        size_t bytes, slack;
-    } arrs[] = {{(void **)&h->part.xperm, sizeof(int) * (size_t)h->n_cols, 0},
-                {(void **)&h->part.rId, sizeof(int) * (size_t)s.dRows, 0},
-                {(void **)&h->part.rowPtr_dd, sizeof(int) * ((size_t)s.dRows + 1), 0},
-                {(void **)&h->part.colInd_dd, sizeof(int) * (size_t)s.nnzRowD, 0},
-                {(void **)&h->part.val_dd, vb * (size_t)s.nnzRowD, 0},
-                {(void **)&h->part.tiles.chunkPtr, sizeof(int) * ((size_t)s.chunkNum + 1), 0},
-                {(void **)&h->part.tiles.AToX, sizeof(int) * (size_t)s.totalFrags * s.fragK, 64},
-                {(void **)&h->part.tiles.fragPtr, sizeof(int) * ((size_t)s.totalFrags + 1), 64},
-                {(void **)&h->part.tiles.fragBit, bb * (size_t)s.totalFrags, 64},
-                {(void **)&h->part.tiles.tcVal, vb * (size_t)s.nnzRowD, 64},
-                {(void **)&h->part.rowPtr_CD, sizeof(int) * ((size_t)h->n_rows + 1), 0},
-                {(void **)&h->part.colInd_CD, sizeof(int) * (size_t)s.nnzCD, 0},
-                {(void **)&h->part.val_CD, vb * (size_t)s.nnzCD, 0}};
-    std::string buf;
-    for (const Arr &a : arrs) {
-        uint64_t n = 0;
-        if (fread(&n, sizeof n, 1, fc.f) != 1 || n != a.bytes) {
-            drop_plan(h);
-            return h->fail(MX_ERR_INVALID, "stored partition: array size does not match its header");
+    const size_t vb = val_bytes(h->dtype);
+    void **dev[PA_COUNT] = {(void **)&h->part.xperm,          (void **)&h->part.rId,
+                            (void **)&h->part.rowPtr_dd,      (void **)&h->part.colInd_dd,
+                            (void **)&h->part.val_dd,         (void **)&h->part.tiles.chunkPtr,
+                            (void **)&h->part.tiles.AToX,     (void **)&h->part.tiles.fragPtr,
+                            (void **)&h->part.tiles.fragBit,  (void **)&h->part.tiles.tcVal,
+                            (void **)&h->part.rowPtr_CD,      (void **)&h->part.colInd_CD,
+                            (void **)&h->part.val_CD};
+    for (int a = 0; a < PA_COUNT; ++a) {
+        const size_t n = pf.arr[a].size();
+        // slack: the tile kernel's bulk copies round up to 16 bytes
+        cudaError_t e = cudaMallocAsync(dev[a], n + 64 + 16, h->stream);
+        if (e == cudaSuccess && n > 0)
+            e = cudaMemcpyAsync(*dev[a], pf.arr[a].data(), n, cudaMemcpyHostToDevice, h->stream);
+        if (e != cudaSuccess) {
+            refuse(MX_ERR_CUDA);
+            return h->cuda_fail(e, "mx_load_partition: upload");
         }
-        HCK(cudaMallocAsync(a.dev, a.bytes + a.slack + 16, h->stream));  // slack: bulk copies round up to 16 bytes
-        if (n == 0) continue;
-        buf.resize(n);
-        if (fread(&buf[0], 1, n, fc.f) != n) {
-            drop_plan(h);
-            return h->fail(MX_ERR_INVALID, "stored partition: truncated file");
-        }
-        HCK(cudaMemcpyAsync(*a.dev, buf.data(), n, cudaMemcpyHostToDevice, h->stream));
-        HCK(cudaStreamSynchronize(h->stream));
     }
+    cudaError_t e = cudaStreamSynchronize(h->stream);  // the host copies go out of scope with pf
     h->part.tiles.dRows = s.dRows;
     h->part.tiles.dCols = s.dCols;
     h->part.tiles.chunkNum = s.chunkNum;
     h->part.tiles.totalFrags = s.totalFrags;
     h->part.tiles.nvals = s.nnzRowD;
-    HCK(hotmask_from_rid(h->part.rId, s.dRows, h->n_rows, &h->part.hotmask, h->stream));
-    HCK(cudaMallocAsync(&h->x_stage, vb * (size_t)(h->n_cols > 0 ? h->n_cols : 1), h->stream));
-    HCK(cudaMallocAsync(&h->y_stage, vb * (size_t)(h->n_rows > 0 ? h->n_rows : 1), h->stream));
+    if (e == cudaSuccess) e = hotmask_from_rid(h->part.rId, s.dRows, h->n_rows, &h->part.hotmask, h->stream);
+    if (e == cudaSuccess) e = cudaMallocAsync(&h->x_stage, vb * (size_t)(h->n_cols > 0 ? h->n_cols : 1), h->stream);
+    if (e == cudaSuccess) e = cudaMallocAsync(&h->y_stage, vb * (size_t)(h->n_rows > 0 ? h->n_rows : 1), h->stream);
+    if (e != cudaSuccess) {
+        refuse(MX_ERR_CUDA);
+        return h->cuda_fail(e, "mx_load_partition");
+    }
     int st = finish_partition(h);
-    if (st != MX_OK) return st;
+    if (st != MX_OK) return refuse(st);
     HCK(cudaStreamSynchronize(h->stream));
     if (stats) *stats = h->stats;
     return MX_OK;
@@ -622,6 +608,11 @@ int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float
     if (ms_best) *ms_best = best;
     if (ms_plain) *ms_plain = plain;
     return MX_OK;
+}
+
+int mx_fragment_count_status(long long total_frags, int dtype) {
+    if (dtype != MX_FP64 && dtype != MX_FP16) return MX_ERR_INVALID;
+    return fragment_count_status(total_frags, frag_k(dtype));
 }
 
 int mx_dims(mx_handle_t h, int *n_rows, int *n_cols, int *nnz) {
@@ -889,13 +880,13 @@ int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *cs
     if (ce == cudaSuccess) {
         for (int i = 0; i < warm + iters && ce == cudaSuccess; ++i) {
             if (i == warm) cudaEventRecord(e0, 0);
-            ce = resid_spmv(dtype, P, d_x, d_scratch, nullptr, nullptr, false, nullptr, 0);
+            ce = resid_spmv(dtype, P, d_x, d_scratch, nullptr, nullptr, false, 0);
         }
         cudaEventRecord(e1, 0);
         cudaEventSynchronize(e1);
         cudaEventElapsedTime(&ms, e0, e1);
         if (ms_per_spmv) *ms_per_spmv = iters > 0 ? ms / iters : 0.0;
-        if (ce == cudaSuccess) ce = resid_spmv(dtype, P, d_x, d_y, nullptr, nullptr, true, nullptr, 0);  // y += A x
+        if (ce == cudaSuccess) ce = resid_spmv(dtype, P, d_x, d_y, nullptr, nullptr, true, 0);  // y += A x
         if (ce == cudaSuccess) ce = cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost);
     }
     resid_plan_free(P, 0);

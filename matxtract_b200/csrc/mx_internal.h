@@ -41,8 +41,9 @@ struct ResidCfg<__half> {
     static constexpr int MINBLOCKS = MX_RESID_MINBLOCKS_FP16;
 };
 
-// Device error word bits.
-enum : int { DEVERR_RESID_SLICE = 1, DEVERR_TILE_RANGE = 2, DEVERR_PARTITION = 4 };
+// Device error word bits: DEVERR_INPUT = an uploaded matrix failed the index check; DEVERR_TILE_RANGE = a bounded wait
+// of the tile kernel on its bulk copies ran out.
+enum : int { DEVERR_INPUT = 1, DEVERR_TILE_RANGE = 2 };
 
 // Plan + buffers of the residual CSR kernel for one CSR matrix that lives on the device.
 struct ResidPlan {
@@ -119,7 +120,7 @@ void resid_plan_free(ResidPlan &plan, cudaStream_t s);
 // (which do not write x); the kernel's first wave may then start while they drain.  Measured: -9 % on the power-law
 // benchmark shape.  Behind the tensor-core tile kernel the same overlap costs 13 %, so it is not used there.
 cudaError_t resid_spmv(int dtype, const ResidPlan &plan, const void *x, void *y, const void *ytile,
-                       const uint32_t *hotmask, bool accumulate, int *dev_err, cudaStream_t s, bool chained = false);
+                       const uint32_t *hotmask, bool accumulate, cudaStream_t s, bool chained = false);
 // carrier[row_map[r]] = sum_r in the accumulate type: runs the core-dense block as CSR (low-fill dispatch)
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &plan, const void *x, void *carrier, const int *row_map,
                                   cudaStream_t s);
@@ -141,6 +142,11 @@ cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, 
                           int *status, cudaStream_t s);
 cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,
                           const void *val_dd, TileArrays &T, int *status, cudaStream_t s);
+// sets DEVERR_INPUT in *dev_err when row_ptr decreases anywhere or a column index is outside [0, n_cols)
+cudaError_t validate_csr(int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind, int *dev_err,
+                         cudaStream_t s);
+// MX_OK when `total_frags` fragments of K columns can be indexed with int32 (fragment ids and x-index slots)
+int fragment_count_status(long long total_frags, int K);
 // bit r set for every r in rId (a stored partition carries rId, not the bitmap)
 cudaError_t hotmask_from_rid(const int *rId, int dRows, int n_rows, uint32_t **hotmask, cudaStream_t s);
 // every buffer of the library comes from the stream-ordered pool: allocate and free on the stream that uses it

@@ -257,6 +257,10 @@ cudaError_t sort_desc_pairs(TempBuf &tmp, const int *kin, int *kout, const int *
     return cub::DeviceRadixSort::SortPairsDescending(tmp.p, bytes, kin, kout, vin, vout, n, 0, 32, s);
 }
 
+struct ToLongLong {
+    __host__ __device__ long long operator()(int v) const { return (long long)v; }
+};
+
 inline int nblk(long long n, int b = 256) { return (int)((n + b - 1) / b); }
 
 template <typename V, typename B>
@@ -290,15 +294,27 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
         PCK(inclusive_sum(tmp, head, H, nnzRowD, s));
     }
     k_frag_count<<<nblk(chunkNum + 1), 256, 0, s>>>(panelOff, H, chunkNum, K, nf);
-    PCK(exclusive_sum(tmp, nf, T.chunkPtr, chunkNum + 1, s));
-    int totalFrags = 0;
-    PCK(cudaMemcpyAsync(&totalFrags, T.chunkPtr + chunkNum, sizeof(int), cudaMemcpyDeviceToHost, s));
-    PCK(cudaStreamSynchronize(s));
-    T.totalFrags = totalFrags;
-    if ((long long)totalFrags * K > 2147483647LL) {
-        *status = MX_ERR_OVERFLOW;
-        totalFrags = 0;
+    // the fragment total is taken in 64 bits first: the int32 scan below is only meaningful when it fits
+    long long *total64 = nullptr, htotal = 0;
+    PCK(sc.alloc(&total64, 1));
+    {
+        size_t bytes = 0;
+        cub::TransformInputIterator<long long, ToLongLong, const int *> it(nf, ToLongLong());
+        PCK(cub::DeviceReduce::Sum(nullptr, bytes, it, total64, chunkNum + 1, s));
+        PCK(tmp.reserve(bytes, s));
+        PCK(cub::DeviceReduce::Sum(tmp.p, bytes, it, total64, chunkNum + 1, s));
     }
+    PCK(cudaMemcpyAsync(&htotal, total64, sizeof(long long), cudaMemcpyDeviceToHost, s));
+    PCK(cudaStreamSynchronize(s));
+    int totalFrags = 0;
+    if (fragment_count_status(htotal, K) != MX_OK) {
+        *status = MX_ERR_OVERFLOW;
+        PCK(cudaMemsetAsync(T.chunkPtr, 0, ((size_t)chunkNum + 1) * sizeof(int), s));
+    } else {
+        totalFrags = (int)htotal;
+        PCK(exclusive_sum(tmp, nf, T.chunkPtr, chunkNum + 1, s));
+    }
+    T.totalFrags = totalFrags;
     PCK(dalloc(&T.AToX, (size_t)totalFrags * K + 8, s));  // +slack: bulk copies round up to 16 bytes
     PCK(dalloc((B **)&T.fragBit, (size_t)totalFrags + 8, s));
     PCK(dalloc(&T.fragPtr, (size_t)totalFrags + 1 + 8, s));
@@ -449,6 +465,14 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
 
 }  // namespace
 
+// The reference indexes fragments, and the K x-index slots of every fragment, with its int32 index type
+// (sparse_AToX_index[chunkPtr[p] * fragK + s], test/test_autotc_spmv.cpp:1384-1404): a panel decomposition whose slot
+// count does not fit is refused rather than wrapped.
+int fragment_count_status(long long total_frags, int K) {
+    if (total_frags < 0 || total_frags + 1 > 2147483647LL || total_frags * K > 2147483647LL) return MX_ERR_OVERFLOW;
+    return MX_OK;
+}
+
 cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st,
                           int *status, cudaStream_t s) {
     if (dtype == MX_FP64) return partition_t<double, uint32_t>(A, tau_c, tau_r, P, st, status, s);
@@ -462,6 +486,28 @@ cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_d
                                                  status, s);
     return tiles_from_dd_t<__half, uint64_t>(dRows, nnzRowD, rowPtr_dd, colInd_dd, (const __half *)val_dd, T, status,
                                              s);
+}
+
+// index check of an uploaded matrix: grid-stride over the row pointers and the column indices
+__global__ void k_validate_csr(const int *__restrict__ row_ptr, const int *__restrict__ col_ind, int n_rows, int n_cols,
+                               int nnz, int *__restrict__ dev_err) {
+    const long long stride = (long long)gridDim.x * blockDim.x, t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    bool bad = false;
+    for (long long r = t0; r < n_rows; r += stride) bad |= __ldg(row_ptr + r + 1) < __ldg(row_ptr + r);
+    for (long long e = t0; e < nnz; e += stride) {
+        const int c = __ldg(col_ind + e);
+        bad |= c < 0 || c >= n_cols;
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(dev_err, DEVERR_INPUT);
+}
+
+cudaError_t validate_csr(int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind, int *dev_err,
+                         cudaStream_t s) {
+    const long long work = std::max<long long>(n_rows, nnz);
+    if (work <= 0) return cudaSuccess;
+    const int grid = (int)std::min<long long>((work + 255) / 256, 148 * 16);
+    k_validate_csr<<<grid, 256, 0, s>>>(row_ptr, col_ind, n_rows, n_cols, nnz, dev_err);
+    return cudaGetLastError();
 }
 
 __global__ void k_hotmask_from_rid(const int *__restrict__ rId, int dRows, uint32_t *__restrict__ hotmask) {

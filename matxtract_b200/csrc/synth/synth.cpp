@@ -13,7 +13,7 @@
 
 #include <cuda_fp16.h>
 
-#include "mx_capi.h"
+#include "mx_synth.h"
 
 namespace {
 
@@ -145,7 +145,7 @@ struct Gen {
 };
 
 void store_val(int dtype, void *val, int64_t p, double v) {
-    if (dtype == MX_FP64)
+    if (dtype == MX_SYNTH_FP64)
         ((double *)val)[p] = v;
     else
         ((__half *)val)[p] = __float2half((float)v);
@@ -156,7 +156,7 @@ void store_val(int dtype, void *val, int64_t p, double v) {
 extern "C" {
 
 int mx_synth_row_lengths(const mx_synth_params *p, int64_t row_begin, int64_t row_end, int *row_ptr_out) {
-    if (!p || !row_ptr_out || row_begin < 0 || row_end > p->n || row_begin > row_end) return MX_ERR_INVALID;
+    if (!p || !row_ptr_out || row_begin < 0 || row_end > p->n || row_begin > row_end) return 1;  // bad argument
     Gen g(*p);
     int64_t rows = row_end - row_begin;
     std::vector<int> len(rows);
@@ -174,15 +174,15 @@ int mx_synth_row_lengths(const mx_synth_params *p, int64_t row_begin, int64_t ro
     row_ptr_out[0] = 0;
     for (int64_t i = 0; i < rows; ++i) {
         acc += len[i];
-        if (acc > 2147483647LL) return MX_ERR_OVERFLOW;
+        if (acc > 2147483647LL) return 5;  // more than INT_MAX entries
         row_ptr_out[i + 1] = (int)acc;
     }
-    return MX_OK;
+    return 0;
 }
 
 int mx_synth_fill(const mx_synth_params *p, int dtype, int64_t row_begin, int64_t row_end, const int *row_ptr,
                   int *col_ind, void *val) {
-    if (!p || !row_ptr || !col_ind || !val) return MX_ERR_INVALID;
+    if (!p || !row_ptr || !col_ind || !val) return 1;  // bad argument
     Gen g(*p);
     int64_t rows = row_end - row_begin;
     int bad = 0;
@@ -206,18 +206,18 @@ int mx_synth_fill(const mx_synth_params *p, int dtype, int64_t row_begin, int64_
             }
         }
     }
-    return bad ? MX_ERR_INVALID : MX_OK;
+    return bad ? 1 : 0;
 }
 
 // x ~ U(-1,1), element i from stream (seed, i): independent of the length requested.
 int mx_synth_vector(uint64_t seed, int dtype, int64_t begin, int64_t end, void *x) {
-    if (!x || begin > end) return MX_ERR_INVALID;
+    if (!x || begin > end) return 1;  // bad argument
 #pragma omp parallel for schedule(static)
     for (int64_t i = begin; i < end; ++i) {
         Rng r(seed ^ 0x5851F42D4C957F2Dull, (uint64_t)i);
         store_val(dtype, x, i - begin, 2.0 * r.uni() - 1.0);
     }
-    return MX_OK;
+    return 0;
 }
 
 }  // extern "C"

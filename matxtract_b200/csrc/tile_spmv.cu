@@ -30,11 +30,9 @@
 #include "device_prims.cuh"
 #include "mx_internal.h"
 
-#ifndef MX_TILE_UNROLL
-#define MX_TILE_UNROLL 4  // fragment pairs per unrolled pass of the FP64 loop (A/B on the block matrix, tile half alone:
-                          // 1: -, 2: 124.6 us, 4: 108.7 us, 8: 114.6 us; explicit operand batches of 8 / 16: 130 / 110 us)
-#endif
-constexpr int TILE_UNROLL = MX_TILE_UNROLL;
+// fragment pairs per unrolled pass of the FP64 loop (A/B on the block matrix, tile half alone: 2: 124.6 us,
+// 4: 108.7 us, 8: 114.6 us; explicit operand batches of 8 / 16: 130 / 110 us)
+constexpr int TILE_UNROLL = 4;
 
 namespace mx {
 namespace {
@@ -146,11 +144,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar) {
     return false;
 }
 
-constexpr int STAGE_WARPS_MAX = 8;
-int g_stage_warps = 4;           // warps per CTA (4 or 8)
+constexpr int STAGE_WARPS = 4;   // warps per CTA (8 measured slower)
 int g_tile_prefetch = -1;        // L2 prefetch distance in CTAs; default 5 per SM (A/B on the block matrix: tile half
                                  // 113.8 -> 108.7 us; 10 per SM 110.1, 20 per SM 122.8), MX_TILE_PREFETCH overrides, 0 = off
-int g_stage_bytes = 16 * 1024;   // target bytes per CTA; a CTA may exceed it by one segment (sweep: 8-64 KB)
+constexpr int STAGE_BYTES_TARGET = 16 * 1024;  // per CTA; a CTA may exceed it by one segment (sweep: 8-64 KB)
 
 // byte layout of a CTA's shared-memory stage; every range starts 16-byte aligned in global AND shared memory
 template <typename B, typename V, int K>
@@ -265,8 +262,8 @@ __device__ __forceinline__ void run_segment(const int4 sd, int s, int lane, cons
     }
 }
 
-template <typename B, typename V, int K, typename OutT, bool ACCUM, int STAGE_WARPS>
-__global__ void __launch_bounds__(STAGE_WARPS * 32)
+template <typename B, typename V, int K, typename OutT, bool ACCUM, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
     tile_kernel_staged(const V *__restrict__ x_d, const int *__restrict__ fragPtr, const B *__restrict__ fragBit,
                        const V *__restrict__ tcVal, const int *__restrict__ AToX, const CtaDesc *__restrict__ desc,
                        const int4 *__restrict__ segDesc, const int *__restrict__ panelFirstSeg,
@@ -303,7 +300,7 @@ __global__ void __launch_bounds__(STAGE_WARPS * 32)
         const uint32_t len[4] = {Ln.nX, Ln.nBit, Ln.nPtr, Ln.nV};
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            for (uint32_t off = threadIdx.x * 128u; off < len[r]; off += STAGE_WARPS * 32 * 128u)
+            for (uint32_t off = threadIdx.x * 128u; off < len[r]; off += NWARPS * 32 * 128u)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(base[r] + off));
     }
     if (!mbar_wait_bounded(bar)) {  // never expected; leaves a mark instead of spinning for ever
@@ -318,7 +315,7 @@ __global__ void __launch_bounds__(STAGE_WARPS * 32)
     int s = d.seg0 + warp;
     int4 sd = s < d.seg1 ? __ldg(segDesc + s) : make_int4(0, 0, 0, -1);
     while (s < d.seg1) {
-        const int sn = s + STAGE_WARPS;
+        const int sn = s + NWARPS;
         const int4 sdn = sn < d.seg1 ? __ldg(segDesc + sn) : make_int4(0, 0, 0, -1);  // next descriptor, early
         run_segment<B, V, K, OutT, ACCUM>(sd, s, lane, sBit, sPtr, sX, sVal, x_d, panelFirstSeg, partial, panelCount,
                                           out, row_map, dRows);
@@ -453,8 +450,6 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
         cudaSuccess)
         return e;
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
-    if (const char *ev = getenv("MX_STAGE_BYTES")) g_stage_bytes = atoi(ev);
-    if (const char *ev = getenv("MX_STAGE_WARPS")) g_stage_warps = atoi(ev) == 4 ? 4 : 8;
     if (const char *ev = getenv("MX_TILE_PREFETCH")) {
         g_tile_prefetch = atoi(ev) > 0 ? atoi(ev) : 0;
     } else if (g_tile_prefetch < 0) {
@@ -463,7 +458,7 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         g_tile_prefetch = 5 * sms;
     }
-    const int STAGE_BYTES = g_stage_bytes;
+    const int STAGE_BYTES = STAGE_BYTES_TARGET;
     P.numCtas = (int)((totalBytes + STAGE_BYTES - 1) / STAGE_BYTES);
     if (P.numCtas < 1) P.numCtas = 1;
     if ((e = cudaMallocAsync(&P.ctaDesc, (size_t)P.numCtas * sizeof(CtaDesc), s)) != cudaSuccess) return e;
@@ -508,12 +503,11 @@ cudaError_t tile_spmv(int dtype, const TilePlan &P, const void *x_d, void *out, 
                       bool accumulate, int *dev_err, cudaStream_t s) {
     if (P.numSegs <= 0) return cudaSuccess;
     if (P.ctaDesc && P.stageBytes > 0 && P.stageBytes <= 200 * 1024) {
-        dim3 sg(P.numCtas), sb(g_stage_warps * 32);
+        dim3 sg(P.numCtas), sb(STAGE_WARPS * 32);
         const size_t smem = (size_t)P.stageBytes;
 #define MX_STAGED(BT, VT, KK, OT, AC, AT)                                                                            \
     do {                                                                                                             \
-        auto kern = g_stage_warps == 4 ? tile_kernel_staged<BT, VT, KK, OT, AC, 4>                                   \
-                                       : tile_kernel_staged<BT, VT, KK, OT, AC, 8>;                                  \
+        auto kern = tile_kernel_staged<BT, VT, KK, OT, AC, STAGE_WARPS>;                                             \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         kern<<<sg, sb, smem, s>>>((const VT *)x_d, P.A.fragPtr, (const BT *)P.A.fragBit, (const VT *)P.A.tcVal,      \
                                   P.A.AToX, (const CtaDesc *)P.ctaDesc, (const int4 *)P.segDesc,                     \

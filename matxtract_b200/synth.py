@@ -11,7 +11,38 @@ from dataclasses import dataclass
 
 import numpy as np
 
+from pathlib import Path
+
 from . import capi
+
+_SYNTH_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmx_synth.so"
+_synth_lib = None
+
+
+class SynthParams(C.Structure):
+    _fields_ = [("kind", C.c_int), ("n", C.c_int64), ("seed", C.c_uint64), ("mean_len", C.c_double),
+                ("zipf_s", C.c_double), ("alpha", C.c_double), ("max_len", C.c_int64), ("local_frac", C.c_double),
+                ("local_halfwidth", C.c_int64), ("blocks_per_row", C.c_int), ("hot_col_frac", C.c_double),
+                ("hot_nnz_frac", C.c_double), ("normal_values", C.c_int)]
+
+
+def synth_lib() -> C.CDLL:
+    """Loads libmx_synth.so: host code only, separate from the GPU library (``include/mx_synth.h``)."""
+    global _synth_lib
+    if _synth_lib is None:
+        if not _SYNTH_LIB_PATH.exists():
+            raise ImportError(f"{_SYNTH_LIB_PATH} is missing: run `python -m matxtract_b200.build`")
+        L = C.CDLL(str(_SYNTH_LIB_PATH))
+        vp = C.c_void_p
+        L.mx_synth_row_lengths.restype = C.c_int
+        L.mx_synth_row_lengths.argtypes = [C.POINTER(SynthParams), C.c_int64, C.c_int64, vp]
+        L.mx_synth_fill.restype = C.c_int
+        L.mx_synth_fill.argtypes = [C.POINTER(SynthParams), C.c_int, C.c_int64, C.c_int64, vp, vp, vp]
+        L.mx_synth_vector.restype = C.c_int
+        L.mx_synth_vector.argtypes = [C.c_uint64, C.c_int, C.c_int64, C.c_int64, vp]
+        _synth_lib = L
+    return _synth_lib
+
 
 UNIFORM, POWERLAW, BLOCK, HOTCOL = 0, 1, 2, 3
 BASE_SEED = 0x4D585452
@@ -78,7 +109,7 @@ def powerlaw_alpha(zipf_s: float, max_len: int, mean: float) -> float:
 _ALPHA_CACHE: dict = {}
 
 
-def params(cfg: Config, n: int | None = None) -> capi.SynthParams:
+def params(cfg: Config, n: int | None = None) -> SynthParams:
     n = cfg.n if n is None else int(n)
     alpha = 0.0
     if cfg.kind == POWERLAW:
@@ -88,13 +119,14 @@ def params(cfg: Config, n: int | None = None) -> capi.SynthParams:
         alpha = _ALPHA_CACHE[key]
     if cfg.kind == BLOCK and n % 8:
         raise ValueError("block-structured matrices need n % 8 == 0")
-    return capi.SynthParams(cfg.kind, n, cfg.seed, cfg.mean_len, cfg.zipf_s, alpha, cfg.max_len, cfg.local_frac,
+    return SynthParams(cfg.kind, n, cfg.seed, cfg.mean_len, cfg.zipf_s, alpha, cfg.max_len, cfg.local_frac,
                             cfg.local_halfwidth, cfg.blocks_per_row, cfg.hot_col_frac, cfg.hot_nnz_frac,
                             int(cfg.normal_values))
 
 
-def generate(cfg: Config | str, n: int | None = None, rows: tuple | None = None, dtype: int | None = None) -> dict:
-    """Rows [rows[0], rows[1]) (default: all) of the n x n matrix of `cfg`, plus the full x.
+def generate(cfg: Config | str, n: int | None = None, rows: tuple | None = None, dtype: int | None = None,
+             with_x: bool = True) -> dict:
+    """Rows [rows[0], rows[1]) (default: all) of the n x n matrix of `cfg`, plus (with_x) the full x.
 
     Returns dict(n, row_begin, row_ptr (relative), col_ind, val, x, nnz, dtype).
     """
@@ -104,7 +136,7 @@ def generate(cfg: Config | str, n: int | None = None, rows: tuple | None = None,
     p = params(cfg, n)
     n = int(p.n)
     r0, r1 = (0, n) if rows is None else rows
-    L = capi.lib()
+    L = synth_lib()
     row_ptr = np.empty(r1 - r0 + 1, np.int32)
     st = L.mx_synth_row_lengths(C.byref(p), r0, r1, capi._ptr(row_ptr))
     if st != 0:
@@ -115,11 +147,26 @@ def generate(cfg: Config | str, n: int | None = None, rows: tuple | None = None,
     st = L.mx_synth_fill(C.byref(p), dtype, r0, r1, capi._ptr(row_ptr), capi._ptr(col_ind), capi._ptr(val))
     if st != 0:
         raise capi.MxError(st, "mx_synth_fill")
-    x = np.empty(n, capi.np_dtype(dtype))
-    st = L.mx_synth_vector(cfg.seed, dtype, 0, n, capi._ptr(x))
-    if st != 0:
-        raise capi.MxError(st, "mx_synth_vector")
+    x = None
+    if with_x:
+        x = np.empty(n, capi.np_dtype(dtype))
+        st = L.mx_synth_vector(cfg.seed, dtype, 0, n, capi._ptr(x))
+        if st != 0:
+            raise capi.MxError(st, "mx_synth_vector")
     return dict(n=n, row_begin=r0, row_ptr=row_ptr, col_ind=col_ind, val=val, x=x, nnz=nnz, dtype=dtype, name=cfg.name)
+
+
+def row_pointers(cfg: Config | str, n: int | None = None) -> np.ndarray:
+    """Row pointers (int32, n+1) of the whole n x n matrix of `cfg`, without its entries: what a rank needs to find
+    the nnz-balanced row range it owns before it generates that range."""
+    if isinstance(cfg, str):
+        cfg = CONFIGS[cfg]
+    p = params(cfg, n)
+    row_ptr = np.empty(int(p.n) + 1, np.int32)
+    st = synth_lib().mx_synth_row_lengths(C.byref(p), 0, int(p.n), capi._ptr(row_ptr))
+    if st != 0:
+        raise capi.MxError(st, "mx_synth_row_lengths")
+    return row_ptr
 
 
 def algorithmic_bytes(n_rows: int, n_cols: int, nnz: int, dtype: int) -> int:

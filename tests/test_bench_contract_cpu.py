@@ -30,6 +30,11 @@ def test_reference_arm_prints_one_contract_line():
     e = d["e2e"]
     assert e["value"] == d["value"] and e["unit"] == d["unit"]
     assert e["h2d_bytes_per_step"] == 0 and e["d2h_bytes_per_step"] == 0
+    # the same `config` keys as the GPU arm prints, and none of the GPU library mapped into the process
+    assert {"workload", "tau", "n", "nnz", "scaling", "l2", "parallelism"} <= set(d["config"])
+    assert d["config"]["n"] == 10000 and d["config"]["nnz"] > 0
+    assert d["native_libs"] and not [p for p in d["native_libs"] if "libmatxtract_b200" in p or "libMatXtract" in p]
+    assert any(p.startswith("oracle/") for p in d["native_libs"])
 
 
 def test_reference_arm_is_silent_on_other_ranks():

@@ -112,3 +112,16 @@ def test_header_is_plain_c(tmp_path):
     assert r.returncode == 0, r.stderr
     sizes = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True).stdout.split()]
     assert sizes == [C.sizeof(capi.PartitionStats), C.sizeof(capi.DistFeatures), C.sizeof(capi.MatrixFeatures)]
+
+
+def test_fragment_count_overflow_rule():
+    """The int32 limit of the fragment format (fragment ids and fragK x-index slots per fragment), on the host."""
+    L = capi.lib()
+    int_max = 2**31 - 1
+    for dtype, k in ((mx.FP64, 4), (mx.FP16, 8)):
+        assert L.mx_fragment_count_status(0, dtype) == 0
+        assert L.mx_fragment_count_status(int_max // k, dtype) == 0          # last total whose slots still fit
+        assert L.mx_fragment_count_status(int_max // k + 1, dtype) == 5      # MX_ERR_OVERFLOW
+        assert L.mx_fragment_count_status(2**40, dtype) == 5
+        assert L.mx_fragment_count_status(-1, dtype) == 5
+    assert L.mx_fragment_count_status(1, 7) == 1                             # unknown value type
