@@ -391,11 +391,15 @@ def run_ours(args):
     st = h.partition(*tau)
     preprocess_ms_cold = st.preprocess_ms  # first call: includes CUDA module loading and memory-pool growth
     st = h.partition(*tau)                 # steady-state cost of the same extraction
+    dd_times = h.dd_executor_times
     if args.dd != "auto":
-        h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR}[args.dd])
+        h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR, "se": mx.DD_SE}[args.dd])
     if args.colspace != "auto":
         h.set_column_space({"permuted": mx.COLSPACE_PERMUTED, "original": mx.COLSPACE_ORIGINAL}[args.colspace])
+    if args.hotx != "auto":
+        h.set_hot_prefix({"off": mx.HOT_OFF, "on": mx.HOT_ON}[args.hotx])
     colspace = h.column_space
+    hot = h.hot_prefix
     stream = torch.cuda.ExternalStream(h.stream, device=dev)
 
     x_host = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).pin_memory()
@@ -695,10 +699,13 @@ def run_ours(args):
         "partition": {k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
         "dd_executor": {1: "tile (tensor cores)", 2: "csr (CUDA cores)", 3: "sparse-encode (tensor cores)"}.get(
             h.dd_executor, "none"),
+        "dd_executor_tuned_ms": {"tile": dd_times[0], "csr": dd_times[1], "sparse_encode": dd_times[2]},
         "column_space": {"in_use": {1: "permuted", 2: "original"}.get(colspace[0], "n/a"),
                          "tuned_ms_permuted": colspace[1], "tuned_ms_original": colspace[2]},
+        "hot_x_prefix": {"columns_in_shared_memory": hot[0], "tuned_ms_with": hot[1], "tuned_ms_without": hot[2]},
         "csr_l2_prefetch_tiles": {"resid": h.csr_prefetch[0], "dd": h.csr_prefetch[1]},
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms, "preprocess_ms_first_call": preprocess_ms_cold,
+        "plan_tuning_ms": st.tuning_ms,
         "ms_dd_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "traffic_note": traffic_note,
@@ -737,9 +744,12 @@ def main():
                     help="N > 1: how y is assembled (auto = the fastest of epilogue / push / nccl, timed at set-up)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the one matrix cut into N slabs (default), weak = N times the rows")
-    ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr"], help="executor of the core-dense block")
+    ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr", "se"],
+                    help="executor of the core-dense block (auto = the fastest of the three, timed at partition time)")
     ap.add_argument("--colspace", default="auto", choices=["auto", "permuted", "original"],
                     help="column numbering used for execution")
+    ap.add_argument("--hotx", default="auto", choices=["auto", "on", "off"],
+                    help="hot-column prefix of x in shared memory (permuted numbering only)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

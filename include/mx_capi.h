@@ -64,6 +64,7 @@ typedef struct {
     double tc_nnz_ratio;                /* nnzRowD / (totalFrags * 8 * fragK), :1376 */
     float preprocess_ms;                /* device time of the whole extraction */
     int active;                         /* 0 when tau = (0,0): no extraction, the residual is the input CSR (:1106,:1638) */
+    float tuning_ms;                    /* host time of the plan-time tuners (timed trial products), not in preprocess_ms */
 } mx_partition_stats;
 
 /* Runs the cascaded extraction on the device: column histogram and tau_c hot-column selection, row
@@ -192,14 +193,17 @@ int mx_csr_prefetch(mx_handle_t h, int *resid_tiles, int *dd_tiles);
  * SpMV time is to be read against it when the gathers, not HBM, bound the product. */
 int mx_stream_gather_floor(mx_handle_t h, const void *x_dev, int warm, int iters, float *ms);
 /* Executor of the core-dense block.  The reference switches between its "dense-unfold" fragment kernel and its
- * "sparse-encode" kernel on nnz and the fragment fill ratio (test/test_autotc_spmv.cpp:1507,1518).  Here:
- * MX_DD_TILE = the tensor-core fragment kernel, MX_DD_CSR = the CUDA-core CSR kernel on the same entries (the
- * role of the sparse-encode path), MX_DD_AUTO = tile kernel when tc_nnz_ratio >= MX_DD_AUTO_FILL.  The partition
- * arrays do not depend on the choice. */
-enum { MX_DD_AUTO = 0, MX_DD_TILE = 1, MX_DD_CSR = 2 };
-#define MX_DD_AUTO_FILL 0.25
+ * "sparse-encode" kernel on nnz and the fragment fill ratio, with thresholds tuned on another GPU
+ * (test/test_autotc_spmv.cpp:1507,1518).  Here: MX_DD_TILE = the tensor-core fragment kernel (du_tcspmv_*),
+ * MX_DD_SE = the tensor-core sparse-encode kernel (se_tcspmv_*: length-sorted rows in zero-padded 8-row slabs, built
+ * on the device), MX_DD_CSR = the CUDA-core CSR kernel on the same entries, MX_DD_AUTO (default) = mx_partition times
+ * the block through all three on the device and keeps the fastest (mx_dd_executor_times reports the three times, 0
+ * where one was not timed).  The partition arrays do not depend on the choice. */
+enum { MX_DD_AUTO = 0, MX_DD_TILE = 1, MX_DD_CSR = 2, MX_DD_SE = 3 };
+#define MX_DD_AUTO_FILL 0.25 /* starting guess before the timing: fragments at least this full go to MX_DD_TILE */
 int mx_set_dd_executor(mx_handle_t h, int mode);
-int mx_dd_executor(mx_handle_t h); /* the one in use: MX_DD_TILE or MX_DD_CSR */
+int mx_dd_executor(mx_handle_t h); /* the one in use: MX_DD_TILE, MX_DD_CSR or MX_DD_SE */
+int mx_dd_executor_times(mx_handle_t h, float *ms_tile, float *ms_csr, float *ms_se);
 /* Column numbering used for EXECUTION (the partition arrays, and what mx_download_partition returns, always use the
  * reference's numbering).  MX_COLSPACE_PERMUTED: hot columns first in density-rank order, as the reference executes
  * (x is permuted on the device at every product; pays when few hot columns carry much of the matrix).
@@ -209,6 +213,16 @@ enum { MX_COLSPACE_AUTO = 0, MX_COLSPACE_PERMUTED = 1, MX_COLSPACE_ORIGINAL = 2 
 int mx_set_column_space(mx_handle_t h, int mode);
 /* the one in use; optionally the two timings (ms per product) of the last automatic choice */
 int mx_column_space(mx_handle_t h, float *ms_permuted, float *ms_original);
+/* Hot-column prefix of x in shared memory.  In the permuted numbering the first dCols entries of x are the densest
+ * columns in rank order (what tau_c selects, test/test_autotc_spmv.cpp:1122-1141); when the CSR kernels run in that
+ * numbering, a persistent variant copies as long a prefix of them as fits one SM's shared memory (1-D bulk copies)
+ * and serves every gather of those columns from there instead of L1 / L2.  MX_HOT_AUTO (default): mx_partition
+ * times the product with and without it and keeps the faster; MX_HOT_OFF / MX_HOT_ON force it.  mx_hot_prefix reports
+ * the prefix length in use (0 = off) and the two timings of the last choice.  The partition arrays do not depend on
+ * it.  The reference gathers x from global memory in every kernel (src/spmv_kernel/cdSpMV.cu:282-300). */
+enum { MX_HOT_AUTO = 0, MX_HOT_OFF = 1, MX_HOT_ON = 2 };
+int mx_set_hot_prefix(mx_handle_t h, int mode);
+int mx_hot_prefix(mx_handle_t h, int *hot_cols, float *ms_with, float *ms_without);
 /* Number of kernel launches one mx_spmv issues for the current matrix / partition. */
 int mx_spmv_launches(mx_handle_t h);
 /* Device error word of the last kernels (0 = none). */
@@ -224,10 +238,15 @@ int mx_cdspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *cs
 int mx_du_tcspmv(int dtype, const int *chunkPtr, const int *fragPtr, const void *fragBit, const void *tcVal,
                  int n_vals, const int *sparse_AToX_index, const void *x, void *y, int dRows, int dCols, int warm,
                  int iters, double *ms_per_spmv);
-/* se_tcspmv_fp64 / se_tcspmv_fp16 (include/MatXtract.h:14-15,30-31): SpMV of the core-dense block given as CSR.
- * Y_val[i] is the result for input row order_rid[i]; this implementation returns the identity order. */
+/* se_tcspmv_fp64 / se_tcspmv_fp16 (include/MatXtract.h:14-15,30-31; src/spmv_kernel/se_tcSpMV_fp64.cu:496-1496):
+ * SpMV of the core-dense block given as CSR through the sparse-encode layout, which is built on the device.  NUM =
+ * warps per CTA, threshold = fill an 8-row slab needs to be stored for the tensor cores (the rest of its rows goes to
+ * the CUDA-core tail), block_longest = length from which a row is split across work units; values <= 0 (threshold
+ * < 0) select the reference's defaults 4 / 0.75 / 256 (test/test_autotc_spmv.cpp:1501-1503).  y[i] is the result for
+ * input row order_rid[i] (rows sorted by length, longest first); the caller un-permutes (:1542). */
 int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColIdx, const void *x, void *y,
-                 int *order_rid, int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv);
+                 int *order_rid, int rowA, int colA, int nnzA, int NUM, double threshold, int block_longest, int warm,
+                 int iters, double *ms_per_spmv);
 
 /* ---- allocation-free CSR SpMV (no counterpart in the reference: every reference wrapper allocates) ---------- */
 /* y = A x for a CSR matrix that is already on the device, for callers that must not allocate device memory at call

@@ -10,8 +10,12 @@ from .capi import (  # noqa: F401
     COLSPACE_PERMUTED,
     DD_AUTO,
     DD_CSR,
+    DD_SE,
     DD_TILE,
     FP16,
+    HOT_AUTO,
+    HOT_OFF,
+    HOT_ON,
     FP64,
     MatXtract,
     MxError,

@@ -7,8 +7,9 @@ from pathlib import Path
 import numpy as np
 
 FP64, FP16 = 0, 1
-DD_AUTO, DD_TILE, DD_CSR = 0, 1, 2
+DD_AUTO, DD_TILE, DD_CSR, DD_SE = 0, 1, 2, 3
 COLSPACE_AUTO, COLSPACE_PERMUTED, COLSPACE_ORIGINAL = 0, 1, 2
+HOT_AUTO, HOT_OFF, HOT_ON = 0, 1, 2
 
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmatxtract_b200.so"
 
@@ -41,7 +42,8 @@ class PartitionStats(C.Structure):
     _fields_ = [("dCols", C.c_int), ("nnzColD", C.c_int), ("sCols", C.c_int), ("nnzColS", C.c_int),
                 ("dRows", C.c_int), ("nnzRowD", C.c_int), ("sRows", C.c_int), ("nnzRowS", C.c_int),
                 ("chunkNum", C.c_int), ("totalFrags", C.c_int), ("nnzCD", C.c_int), ("fragK", C.c_int),
-                ("tc_nnz_ratio", C.c_double), ("preprocess_ms", C.c_float), ("active", C.c_int)]
+                ("tc_nnz_ratio", C.c_double), ("preprocess_ms", C.c_float), ("active", C.c_int),
+                ("tuning_ms", C.c_float)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k, _ in self._fields_}
@@ -91,10 +93,13 @@ SYMBOLS = {
     "mx_dd_executor": (_i, [_vp]),
     "mx_set_column_space": (_i, [_vp, _i]),
     "mx_column_space": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mx_set_hot_prefix": (_i, [_vp, _i]),
+    "mx_hot_prefix": (_i, [_vp, _ip, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_device_error": (_i, [_vp, _ip]),
     "mx_cdspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d), C.POINTER(_d)]),
     "mx_du_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_d)]),
-    "mx_se_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_d)]),
+    "mx_se_tcspmv": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _d, _i, _i, _i, C.POINTER(_d)]),
+    "mx_dd_executor_times": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_csr_spmv_static": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
 }
 
@@ -299,9 +304,27 @@ class MatXtract:
         m = lib().mx_column_space(self._h, C.byref(a), C.byref(b))
         return m, a.value, b.value
 
+    def set_hot_prefix(self, mode: int):
+        """0 = auto (timed at partition time), 1 = off, 2 = on: hot-column prefix of x in shared memory."""
+        self._ck(lib().mx_set_hot_prefix(self._h, mode))
+
+    @property
+    def hot_prefix(self):
+        """(columns of x held in shared memory, 0 = off; ms per product with; ms per product without)."""
+        n, a, b = C.c_int(), C.c_float(), C.c_float()
+        self._ck(lib().mx_hot_prefix(self._h, C.byref(n), C.byref(a), C.byref(b)))
+        return n.value, a.value, b.value
+
     @property
     def dd_executor(self) -> int:
         return lib().mx_dd_executor(self._h)
+
+    @property
+    def dd_executor_times(self):
+        """ms of the core-dense block alone through (tile, csr, sparse-encode) at the last automatic choice."""
+        a, b, c = C.c_float(), C.c_float(), C.c_float()
+        self._ck(lib().mx_dd_executor_times(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
 
     @property
     def stream(self) -> int:
@@ -378,8 +401,9 @@ def du_tcspmv(dtype, chunkPtr, fragPtr, fragBit, tcVal, AToX, x_d, y, dRows, war
     return y, ms.value
 
 
-def se_tcspmv(dtype, val, row_ptr, col_ind, x_d, warm=0, iters=0):
-    """SpMV of a core-dense block given as CSR (host arrays).  Mirror of se_tcspmv_fp64 / se_tcspmv_fp16."""
+def se_tcspmv(dtype, val, row_ptr, col_ind, x_d, warm=0, iters=0, num=4, threshold=0.75, block_longest=256):
+    """SpMV of a core-dense block given as CSR (host arrays) through the sparse-encode layout.  Mirror of
+    se_tcspmv_fp64 / se_tcspmv_fp16: returns (y, order, ms) with y[i] the result of input row order[i]."""
     vdt = np_dtype(dtype)
     val, row_ptr, col_ind, x_d = _c(val, vdt), _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(x_d, vdt)
     rows = len(row_ptr) - 1
@@ -387,7 +411,7 @@ def se_tcspmv(dtype, val, row_ptr, col_ind, x_d, warm=0, iters=0):
     order = np.empty(rows, np.int32)
     ms = C.c_double()
     _raise(lib().mx_se_tcspmv(dtype, _ptr(val), _ptr(row_ptr), _ptr(col_ind), _ptr(x_d), _ptr(y), _ptr(order), rows,
-                              len(x_d), len(col_ind), warm, iters, C.byref(ms)))
+                              len(x_d), len(col_ind), num, threshold, block_longest, warm, iters, C.byref(ms)))
     return y, order, ms.value
 
 

@@ -53,6 +53,7 @@ enum OutMode : int {
     OUT_Y_PEERS = 3   // y_peer[g][row_offset + r] = sum for every GPU g of the box: the y all-gather, fused
 };
 constexpr int MAX_PEERS = 8;
+constexpr int PEER_VEC_FLAG = 0x100;
 
 // tile_row[t] = number of (non-empty) rows whose end lies at or before the first non-zero of tile t
 __global__ void tile_row_kernel(const int *__restrict__ cPtr, int m_rows, int nnz, int tile_nnz, int num_tiles,
@@ -107,6 +108,9 @@ struct RowOut {
     // the same y buffers, or null.  A member of its own changed the register allocation of every variant of the
     // kernel (all up to the launch-bound cap) and cost 4 % on the single-GPU product.
     __device__ __forceinline__ V *multicast() const { return reinterpret_cast<V *>(carrier_out); }
+    // OUT_Y_PEERS: n_peers carries PEER_VEC_FLAG when every peer buffer is 16-byte aligned (16-byte row vectors allowed)
+    __device__ __forceinline__ int peers() const { return n_peers & 0xff; }
+    __device__ __forceinline__ bool vec_ok() const { return (n_peers & PEER_VEC_FLAG) != 0; }
 };
 
 // one store to a multicast address: the switch writes it into every GPU's copy of the buffer
@@ -133,7 +137,61 @@ template <typename V>
 __device__ __forceinline__ void store_peers(const RowOut<V> &o, int r, typename AccOf<V>::T v) {
 #pragma unroll
     for (int g = 0; g < MAX_PEERS; ++g)
-        if (g < o.n_peers) from_acc(v, o.peer_y[g] + o.row_offset + r);
+        if (g < o.peers()) from_acc(v, o.peer_y[g] + o.row_offset + r);
+}
+
+// The y exchange of a tile's finished rows as 16-byte vectors.  `stage[q]` holds the final value (value type) of the
+// q-th row that ends in the tile, q in [qb, nEmit); rowOf(q) is its row index in this GPU's slab.  Rows of a tile are
+// consecutive unless rows without entries lie between them, so the rows are cut into groups of VEC = 16 / sizeof(V)
+// that start at a 16-byte boundary of y; a group whose rows are consecutive leaves as ONE 16-byte store per GPU (a
+// warp then writes 512 contiguous bytes per GPU), the ragged head and tail and any group broken by a gap as scalars.
+template <typename V, typename RowOf>
+__device__ __forceinline__ void store_rows_peers_vec(const RowOut<V> &o, const V *stage, int qb, int nEmit, int tid,
+                                                     int nthreads, RowOf rowOf) {
+    constexpr int VEC = 16 / (int)sizeof(V);
+    const int n = nEmit - qb;
+    if (n <= 0) return;
+    const long long g0 = o.row_offset + rowOf(qb);
+    int lead = (int)((VEC - (g0 & (VEC - 1))) & (VEC - 1));
+    if (lead > n) lead = n;
+    const int nGroups = (n - lead) / VEC, tail0 = qb + lead + nGroups * VEC;
+    for (int i = tid; i < nGroups; i += nthreads) {
+        const int qs = qb + lead + i * VEC;
+        const int rf = rowOf(qs), rl = rowOf(qs + VEC - 1);
+        if (rl - rf == VEC - 1 && ((o.row_offset + rf) & (VEC - 1)) == 0) {
+            int4 pk;
+            if constexpr (sizeof(V) == 8) {
+                const double a = stage[qs], b = stage[qs + 1];
+                pk.x = __double2loint(a), pk.y = __double2hiint(a), pk.z = __double2loint(b), pk.w = __double2hiint(b);
+            } else {
+                unsigned u[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) u[j] = (unsigned)__half_as_ushort(stage[qs + j]);
+                pk.x = (int)(u[0] | (u[1] << 16)), pk.y = (int)(u[2] | (u[3] << 16));
+                pk.z = (int)(u[4] | (u[5] << 16)), pk.w = (int)(u[6] | (u[7] << 16));
+            }
+#pragma unroll
+            for (int g = 0; g < MAX_PEERS; ++g)
+                if (g < o.peers()) *reinterpret_cast<int4 *>(o.peer_y[g] + o.row_offset + rf) = pk;
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                const long long at = o.row_offset + rowOf(qs + j);
+#pragma unroll
+                for (int g = 0; g < MAX_PEERS; ++g)
+                    if (g < o.peers()) o.peer_y[g][at] = stage[qs + j];
+            }
+        }
+    }
+    // ragged ends: rows [qb, qb + lead) and [tail0, nEmit)
+    const int nEnds = lead + (nEmit - tail0);
+    for (int i = tid; i < nEnds; i += nthreads) {
+        const int q = i < lead ? qb + i : tail0 + (i - lead);
+        const long long at = o.row_offset + rowOf(q);
+#pragma unroll
+        for (int g = 0; g < MAX_PEERS; ++g)
+            if (g < o.peers()) o.peer_y[g][at] = stage[q];
+    }
 }
 
 template <typename V, bool HAS_TILE, int MODE>
@@ -216,11 +274,12 @@ static bool chain_enabled() {
 }
 
 template <typename... KArgs, typename... Args>
-cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, bool chained, Args... args) {
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, bool chained, size_t smem,
+                           Args... args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute at{};
     at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -230,27 +289,57 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cuda
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
-template <typename V, int IPT, bool HAS_TILE, int MODE>
-__global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
-    resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
-                 const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
-                 typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz,
-                 int prefetchTiles) {
+// Shared-memory working set of one tile (one per CTA in the one-tile-per-CTA kernel, one per thread group in the
+// persistent kernel).
+template <typename A, int T, int NW>
+struct __align__(16) TileSmem {
+    static constexpr int PADW = 16 / (int)sizeof(A);
+    A sp[T + (T / 16) * PADW];  // products, padded; reused for the sums of the rows that end in the tile
+    unsigned sFlag[T / 32];     // bit i set: a row ends after the tile's i-th non-zero
+    int sFirst[T / 32];         // lowest row (relative) that ends inside the 32-nnz word
+    A warpTail[NW];
+    int warpOpen[NW];
+};
+
+// barrier over the RESID_THREADS threads that work on one tile: the whole CTA, or one group of a persistent CTA
+// (named barriers 1..GROUPS)
+template <int GROUPS>
+__device__ __forceinline__ void tile_sync(int grp) {
+    if constexpr (GROUPS == 1)
+        __syncthreads();
+    else
+        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(RESID_THREADS) : "memory");
+}
+
+// x[c]: from the shared-memory copy of the hot-column prefix when the kernel holds one, else through the read-only path
+template <typename V, bool HOTX>
+__device__ __forceinline__ V load_x(const V *__restrict__ x, const V *xs, int hotCols, int c) {
+    if constexpr (HOTX) {
+        if (c < hotCols) return xs[c];
+    }
+    return __ldg(x + c);
+}
+
+// One tile (T consecutive non-zeros) of the product, by the RESID_THREADS threads tid = 0..RESID_THREADS-1.
+template <typename V, int IPT, bool HAS_TILE, int MODE, int GROUPS, bool HOTX>
+__device__ __forceinline__ void resid_tile(const int t, const int tid, const int grp, const int numTiles,
+                                           TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32> &sm,
+                                           const V *xs, const int hotCols, const int *__restrict__ cPtr,
+                                           const int *__restrict__ colInd, const V *__restrict__ val,
+                                           const V *__restrict__ x, const RowOut<V> &out,
+                                           const int *__restrict__ tileRow, typename AccOf<V>::T *__restrict__ carry,
+                                           typename AccOf<V>::T *__restrict__ head, int nnz, int prefetchTiles) {
     using A = typename AccOf<V>::T;
     constexpr int THREADS = RESID_THREADS;
     constexpr int T = THREADS * IPT;
-    constexpr int NW = THREADS / 32;
-    constexpr int PADW = 16 / (int)sizeof(A);
-    __shared__ __align__(16) A sp[T + (T / 16) * PADW];  // products, padded
+    A *const sp = sm.sp;
     A *const ysum = sp;  // sums of the rows that end in this tile: reuses the buffer once the products are in registers
-    __shared__ unsigned sFlag[T / 32];                   // bit i set: a row ends after the tile's i-th non-zero
-    __shared__ int sFirst[T / 32];                       // lowest row (relative) that ends inside the 32-nnz word
-    __shared__ A warpTail[NW];
-    __shared__ int warpOpen[NW];
-
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    unsigned *const sFlag = sm.sFlag;
+    int *const sFirst = sm.sFirst;
+    A *const warpTail = sm.warpTail;
+    int *const warpOpen = sm.warpOpen;
+    const int lane = tid & 31, w = tid >> 5;
     const int base = t * T;  // nnz < 2^31, so base fits
-    dep_release();  // the fix-up launch may become resident; it waits for this grid to finish
     const int cnt = min(T, nnz - base);
 
     // ---- phase A: lane <-> consecutive non-zeros: coalesced streams, and gathers that coalesce on runs of
@@ -275,7 +364,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     }
     if (prefetchTiles > 0) {  // ask L2 for the streams of the tile that a CTA of the next wave will read
         const int tp = t + prefetchTiles;
-        if (tp + 1 < (int)gridDim.x) {
+        if (tp + 1 < numTiles) {
             constexpr int CL = T * 4 / 128, VL = T * (int)sizeof(V) / 128;
             const char *pc = reinterpret_cast<const char *>(colInd + (size_t)tp * T);
             const char *pv = reinterpret_cast<const char *>(val + (size_t)tp * T);
@@ -299,11 +388,11 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
         sFirst[i] = INT_MAX;
     }
 #pragma unroll
-    for (int j = 0; j < IPT; ++j) sp[pidx<A>(tid + j * THREADS)] = v[j] * to_acc(__ldg(x + c[j]));
+    for (int j = 0; j < IPT; ++j) sp[pidx<A>(tid + j * THREADS)] = v[j] * to_acc(load_x<V, HOTX>(x, xs, hotCols, c[j]));
     const bool headOpen = headPtr < base;
     const int q0 = tid + (headOpen ? 1 : 0);  // the row this thread stores first in the epilogue
     const int rz = (out.nzRow && q0 < nEmit) ? __ldg(out.nzRow + r0 + q0) : r0 + q0;
-    __syncthreads();
+    tile_sync<GROUPS>(grp);
     if (e0 >= 0) {
         atomicOr(&sFlag[e0 >> 5], 1u << (e0 & 31));
         atomicMin(&sFirst[e0 >> 5], tid);
@@ -317,7 +406,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
         atomicOr(&sFlag[e >> 5], 1u << (e & 31));
         atomicMin(&sFirst[e >> 5], k);
     }
-    __syncthreads();
+    tile_sync<GROUPS>(grp);
 
     // ---- phase B: every thread owns IPT consecutive products ----
     const int a = tid * IPT;
@@ -347,7 +436,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     const bool hasEnd = mask != 0u;
     // row (relative to r0) closed by this thread's first set bit
     const int k0 = sFirst[a >> 5] + __popc(word & ((1u << (a & 31)) - 1u));
-    __syncthreads();  // every product is in registers: the buffer now holds row sums
+    tile_sync<GROUPS>(grp);  // every product is in registers: the buffer now holds row sums
     int k = k0;
     A acc = A(0);
 #pragma unroll
@@ -376,7 +465,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
         warpTail[w] = sv;
         warpOpen[w] = hm == 0u;
     }
-    __syncthreads();
+    tile_sync<GROUPS>(grp);
     A cv = A(0);  // tails left by earlier warps for the row that is open at this warp's start
     for (int u = w - 1; u >= 0; --u) {
         cv += warpTail[u];
@@ -390,7 +479,7 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     if (hasEnd) ysum[k0] += pv;  // the first row this thread closed began in earlier threads
     dep_wait();  // from here on: global writes, and the tile half's carrier is read
     if (tid == THREADS - 1) carry[t] = sv + (upto == 0u ? cv : A(0));
-    __syncthreads();
+    tile_sync<GROUPS>(grp);
 
     // ---- coalesced epilogue: one row per thread per pass ----
     if (headOpen && nEmit > 0 && tid == 0) head[t] = ysum[0];  // the fix-up kernel finishes rows that span tiles
@@ -410,10 +499,97 @@ __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
             return;
         }
     }
+    if constexpr (MODE == OUT_Y_PEERS) {
+        // plain peer stores: stage the tile's finished rows in the value type, then send 16-byte vectors.  FP64 rows
+        // are staged in place; FP16 rows go to the padding tail of the product buffer (T/2 halves), so a tile that
+        // closes more rows than that keeps the one-row-per-thread path below.
+        constexpr bool IN_PLACE = sizeof(V) == sizeof(A);
+        const int qb = headOpen ? 1 : 0;
+        if (out.vec_ok() && !out.multicast() && (IN_PLACE || nEmit <= T / 2)) {
+            V *stage = IN_PLACE ? reinterpret_cast<V *>(ysum) : reinterpret_cast<V *>(sp + T);
+            auto rowOf = [&](int q) { return out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q; };
+            for (int q = q0; q < nEmit; q += THREADS) {
+                const int r = q == q0 ? rz : rowOf(q);
+                A v = row_value<V, HAS_TILE, MODE>(out, r, ysum[q]);
+                V o;
+                from_acc(v, &o);
+                stage[q] = o;
+            }
+            tile_sync<GROUPS>(grp);
+            store_rows_peers_vec<V>(out, stage, qb, nEmit, tid, THREADS, rowOf);
+            return;
+        }
+    }
     if (q0 < nEmit) store_row<V, HAS_TILE, MODE>(out, rz, ysum[q0]);
     for (int q = q0 + THREADS; q < nEmit; q += THREADS) {
         const int r = out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q;
         store_row<V, HAS_TILE, MODE>(out, r, ysum[q]);
+    }
+}
+
+
+template <typename V, int IPT, bool HAS_TILE, int MODE>
+__global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
+    resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
+                 const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
+                 typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz,
+                 int prefetchTiles) {
+    __shared__ TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32> sm;
+    dep_release();  // the fix-up launch may become resident; it waits for this grid to finish
+    resid_tile<V, IPT, HAS_TILE, MODE, 1, false>(blockIdx.x, threadIdx.x, 0, (int)gridDim.x, sm, nullptr, 0, cPtr,
+                                                 colInd, val, x, out, tileRow, carry, head, nnz, prefetchTiles);
+}
+
+// The same product with the hot-column prefix of x in shared memory.  In the extraction's column numbering the first
+// dCols entries of x are the densest columns in rank order, so a prefix of them that fits one SM's shared memory can
+// serve every gather of those columns without touching L1 or L2.  One persistent CTA per SM copies the prefix once
+// (1-D bulk copies completing on an mbarrier, bounded wait) and then its HOTX_GROUPS groups of RESID_THREADS threads
+// each run tiles like the CTAs of resid_kernel, synchronising on a named barrier of their own.
+template <typename V>
+struct HotxCfg;
+template <>
+struct HotxCfg<__half> {
+    static constexpr int GROUPS = 6;
+};
+template <>
+struct HotxCfg<double> {
+    static constexpr int GROUPS = 4;
+};
+constexpr int HOTX_SMEM_LIMIT = 227 * 1024;
+
+template <typename V, int IPT, bool HAS_TILE, int MODE>
+__global__ void __launch_bounds__(RESID_THREADS *HotxCfg<V>::GROUPS, 1)
+    resid_hotx_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
+                      const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
+                      typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz,
+                      int prefetchTiles, int numTiles, int hotCols, int *__restrict__ devErr) {
+    constexpr int GROUPS = HotxCfg<V>::GROUPS;
+    using TS = TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32>;
+    extern __shared__ __align__(16) unsigned char dyn[];
+    uint64_t *bar = reinterpret_cast<uint64_t *>(dyn);  // first 16 bytes
+    V *xs = reinterpret_cast<V *>(dyn + 16);
+    const uint32_t xbytes = (uint32_t)hotCols * (uint32_t)sizeof(V);  // a multiple of 16 (the host rounds hotCols)
+    const int grp = threadIdx.x / RESID_THREADS, tid = threadIdx.x % RESID_THREADS;
+    TS &sm = reinterpret_cast<TS *>(dyn + 16 + xbytes)[grp];
+    dep_release();
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(xbytes) : "memory");
+        constexpr uint32_t CHUNK = 32 * 1024;
+        for (uint32_t off = 0; off < xbytes; off += CHUNK)
+            bulk_g2s(reinterpret_cast<unsigned char *>(xs) + off, reinterpret_cast<const unsigned char *>(x) + off,
+                     min(CHUNK, xbytes - off), bar);
+    }
+    __syncthreads();  // the barrier is initialised before anyone polls it
+    if (!mbar_wait_bounded(bar)) {  // never expected; leaves a mark instead of spinning for ever
+        if (threadIdx.x == 0 && devErr) atomicOr(devErr, DEVERR_TILE_RANGE);
+        return;
+    }
+    for (int t = blockIdx.x * GROUPS + grp; t < numTiles; t += (int)gridDim.x * GROUPS) {
+        resid_tile<V, IPT, HAS_TILE, MODE, GROUPS, true>(t, tid, grp, numTiles, sm, xs, hotCols, cPtr, colInd, val, x,
+                                                         out, tileRow, carry, head, nnz, prefetchTiles);
+        tile_sync<GROUPS>(grp);  // the group's buffers are free for its next tile
     }
 }
 
@@ -448,24 +624,43 @@ __global__ void map_indices_kernel(const int *__restrict__ in, const int *__rest
     if (i < n) out[i] = __ldg(map + __ldg(in + i));
 }
 
-// this GPU's finished slab -> the same rows of every other GPU's y (16-byte peer stores over NVLink)
-__global__ void peer_push_kernel(const int4 *__restrict__ src, int4 *const *__restrict__ dst_table, long long n16,
-                                 int n_dst) {
-    int4 *dst = dst_table[blockIdx.y];
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) dst[i] = __ldg(src + i);
-}
-__global__ void peer_push_bytes_kernel(const unsigned char *__restrict__ src, unsigned char *const *__restrict__ dst_table,
-                                       long long nbytes) {
+// this GPU's finished slab -> the same rows of every other GPU's y over NVLink: 16-byte stores for the part between
+// the first and the last 16-byte boundary, single bytes for the ragged ends (a slab cut at an nnz-balanced row boundary
+// rarely starts on one).  aligned = every destination has the source's alignment modulo 16; otherwise all by bytes.
+__global__ void peer_push_kernel(const unsigned char *__restrict__ src, unsigned char *const *__restrict__ dst_table,
+                                 long long nbytes, int aligned) {
     unsigned char *dst = dst_table[blockIdx.y];
+    long long head = aligned ? (long long)((16u - (unsigned)((uintptr_t)src & 15u)) & 15u) : nbytes;
+    if (head > nbytes) head = nbytes;
+    const long long n16 = (nbytes - head) / 16, tail0 = head + n16 * 16;
+    const int4 *s16 = reinterpret_cast<const int4 *>(src + head);
+    int4 *d16 = reinterpret_cast<int4 *>(dst + head);
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += stride) dst[i] = src[i];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) d16[i] = __ldg(s16 + i);
+    if (aligned && blockIdx.x == 0) {
+        for (long long i = threadIdx.x; i < head; i += blockDim.x) dst[i] = src[i];
+        for (long long i = tail0 + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
+    } else if (!aligned) {
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += stride) dst[i] = src[i];
+    }
 }
 
 template <typename V>
 __global__ void gather_kernel(const V *__restrict__ x, const int *__restrict__ perm, V *__restrict__ out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __ldg(x + __ldg(perm + i));
+}
+
+template <typename V>
+size_t hotx_smem_bytes(int hotCols) {
+    using TS = TileSmem<typename AccOf<V>::T, RESID_THREADS * ResidCfg<V>::IPT, RESID_THREADS / 32>;
+    return 16 + (size_t)hotCols * sizeof(V) + sizeof(TS) * HotxCfg<V>::GROUPS;
+}
+
+int hotx_sm_count() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
 }
 
 template <typename V>
@@ -484,19 +679,39 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     out.nzRow = P.nz_row;
     out.n_peers = n_peers;
     out.row_offset = row_offset;
-    for (int g = 0; g < MAX_PEERS; ++g) out.peer_y[g] = g < n_peers ? (V *)peers[g] : nullptr;
+    bool aligned16 = n_peers > 0;
+    for (int g = 0; g < MAX_PEERS; ++g) {
+        out.peer_y[g] = g < n_peers ? (V *)peers[g] : nullptr;
+        if (g < n_peers && ((uintptr_t)peers[g] & 15u) != 0) aligned16 = false;
+    }
+    if (aligned16) out.n_peers |= PEER_VEC_FLAG;
     dim3 grid(P.num_tiles), block(RESID_THREADS);
     const int fwork = P.num_tiles - 1 > P.n_empty ? P.num_tiles - 1 : P.n_empty;
     const int fgrid = (fwork + 127) / 128;
     cudaError_t le = cudaSuccess;
+    // hot-column prefix of x in shared memory (persistent kernel): only where the plan says so and x is 16-byte aligned
+    const int hot = (P.hot_cols > 0 && ((uintptr_t)x & 15u) == 0 && mode != OUT_Y_ACCUM) ? P.hot_cols : 0;
 #define MX_LAUNCH(HT, MD)                                                                                           \
     do {                                                                                                            \
-        le = launch_chained(resid_kernel<V, IPT, HT, MD>, grid, block, s, chained, P.c_ptr, P.col_ind,              \
-                            (const V *)P.val, (const V *)x, out, (const int *)P.tile_row, (A *)P.carry,            \
-                            (A *)P.head, P.nnz, P.prefetch_tiles);                                                  \
+        if (hot > 0) {                                                                                              \
+            auto kern = resid_hotx_kernel<V, IPT, HT, MD>;                                                          \
+            const size_t smem = hotx_smem_bytes<V>(hot);                                                            \
+            le = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
+            if (le == cudaSuccess) {                                                                                \
+                const int pgrid = std::min(hotx_sm_count(), (P.num_tiles + HotxCfg<V>::GROUPS - 1) / HotxCfg<V>::GROUPS); \
+                le = launch_chained(kern, dim3(pgrid), dim3(RESID_THREADS * HotxCfg<V>::GROUPS), s, chained, smem,  \
+                                    P.c_ptr, P.col_ind, (const V *)P.val, (const V *)x, out,                        \
+                                    (const int *)P.tile_row, (A *)P.carry, (A *)P.head, P.nnz, P.prefetch_tiles,    \
+                                    P.num_tiles, hot, P.dev_err);                                                    \
+            }                                                                                                       \
+        } else {                                                                                                    \
+            le = launch_chained(resid_kernel<V, IPT, HT, MD>, grid, block, s, chained, 0, P.c_ptr, P.col_ind,       \
+                                (const V *)P.val, (const V *)x, out, (const int *)P.tile_row, (A *)P.carry,        \
+                                (A *)P.head, P.nnz, P.prefetch_tiles);                                              \
+        }                                                                                                           \
         if (le == cudaSuccess && fgrid > 0)                                                                         \
-            le = launch_chained(resid_fixup_kernel<V, IPT, HT, MD>, dim3(fgrid), dim3(128), s, true, P.c_ptr, out,  \
-                                (const int *)P.tile_row, (const A *)P.carry, (const A *)P.head, P.m_rows,           \
+            le = launch_chained(resid_fixup_kernel<V, IPT, HT, MD>, dim3(fgrid), dim3(128), s, true, 0, P.c_ptr,    \
+                                out, (const int *)P.tile_row, (const A *)P.carry, (const A *)P.head, P.m_rows,      \
                                 P.num_tiles, (const int *)P.empty_row, P.n_empty);                                  \
     } while (0)
     if (mode == OUT_CARRIER)
@@ -590,6 +805,15 @@ void resid_plan_free(ResidPlan &P, cudaStream_t s) {
     P.tile_row = P.c_ptr_own = P.nz_row = P.empty_row = nullptr;
     P.c_ptr = nullptr;
     P.carry = P.head = nullptr;
+}
+
+int resid_hot_cols_budget(int dtype, int d_cols) {
+    const size_t fixed = dtype == MX_FP64 ? hotx_smem_bytes<double>(0) : hotx_smem_bytes<__half>(0);
+    const size_t vb = val_bytes(dtype);
+    long long cols = (long long)((HOTX_SMEM_LIMIT - fixed) / vb);
+    if (cols > d_cols) cols = d_cols;
+    cols -= cols % (long long)(16 / vb);
+    return cols >= 256 ? (int)cols : 0;
 }
 
 int resid_launches(const ResidPlan &P) { return (P.num_tiles > 1 || P.n_empty > 0) ? 2 : 1; }
@@ -831,16 +1055,14 @@ extern "C" int mx_peer_push(int dtype, void *const *y_peers, int n_peers, int se
     }
     const unsigned char *src = static_cast<const unsigned char *>(y_peers[self]) + (size_t)row_offset * vb;
     const long long nbytes = n_rows * (long long)vb;
-    if (((uintptr_t)src & 15) == 0 && (nbytes & 15) == 0) {
-        const long long n16 = nbytes / 16;
-        int gx = (int)std::min<long long>((n16 + 255) / 256, 148 * 4 / nd + 1);
-        peer_push_kernel<<<dim3(gx, nd), 256, 0, s>>>(reinterpret_cast<const int4 *>(src),
-                                                      reinterpret_cast<int4 *const *>(table_dev), n16, nd);
-    } else {
-        int gx = (int)std::min<long long>((nbytes + 255) / 256, 148 * 4 / nd + 1);
-        peer_push_bytes_kernel<<<dim3(gx, nd), 256, 0, s>>>(src, reinterpret_cast<unsigned char *const *>(table_dev),
-                                                            nbytes);
-    }
+    int aligned = 1;
+    for (int d = 0; d < nd; ++d)
+        if ((((uintptr_t)host_tab[d] ^ (uintptr_t)src) & 15u) != 0) aligned = 0;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long units = aligned ? (nbytes + 15) / 16 : nbytes;
+    const int gx = (int)std::max<long long>(1, std::min<long long>((units + 255) / 256, sms * 4 / nd + 1));
+    peer_push_kernel<<<dim3(gx, nd), 256, 0, s>>>(src, reinterpret_cast<unsigned char *const *>(table_dev), nbytes, aligned);
     if (cudaGetLastError() != cudaSuccess) return MX_ERR_CUDA;
     return MX_OK;
 }

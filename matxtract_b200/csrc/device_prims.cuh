@@ -2,6 +2,7 @@
 #pragma once
 #include <cub/cub.cuh>
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace mx {
 
@@ -41,6 +42,31 @@ inline cudaError_t inclusive_sum(TempBuf &tmp, const InT *in, OutT *out, int n, 
     if (e != cudaSuccess) return e;
     if ((e = tmp.reserve(bytes, s)) != cudaSuccess) return e;
     return cub::DeviceScan::InclusiveSum(tmp.p, bytes, in, out, n, s);
+}
+
+// ---- 1-D bulk copies (TMA) into shared memory, completing on an mbarrier; no multicast ----
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// waits for phase 0 of the barrier; gives up after a bounded number of polls (returns false)
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar) {
+    const uint32_t a = smem_u32(bar);
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(0u)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
 }
 
 }  // namespace mx

@@ -64,9 +64,9 @@ void du_tcspmv_fp64(indT *chunkPtr, std::vector<int> fragPtr, std::vector<uint32
           "du_tcspmv_fp64");
 }
 void se_tcspmv_fp64(valT *csrValA, indT *csrRowPtrA, int *csrColIdxA, valT *X_val, valT *Y_val, int *order_rid,
-                    int rowA, int colA, indT nnzA, int, double, int, double *tcTime) {
-    check(mx_se_tcspmv(kDtype, csrValA, csrRowPtrA, csrColIdxA, X_val, Y_val, order_rid, rowA, colA, nnzA, kWarm, kIters,
-                       tcTime),
+                    int rowA, int colA, indT nnzA, int NUM, double threshold, int block_longest, double *tcTime) {
+    check(mx_se_tcspmv(kDtype, csrValA, csrRowPtrA, csrColIdxA, X_val, Y_val, order_rid, rowA, colA, nnzA, NUM,
+                       threshold, block_longest, kWarm, kIters, tcTime),
           "se_tcspmv_fp64");
 }
 #else
@@ -77,9 +77,9 @@ void du_tcspmv_fp16_v2(indT *chunkPtr, std::vector<int> fragPtr, std::vector<uin
           "du_tcspmv_fp16_v2");
 }
 void se_tcspmv_fp16(valT *csrValA, indT *csrRowPtrA, int *csrColIdxA, valT *X_val, valT *Y_val, int *order_rid,
-                    int rowA, int colA, indT nnzA, int, double, int, double *tcTime) {
-    check(mx_se_tcspmv(kDtype, csrValA, csrRowPtrA, csrColIdxA, X_val, Y_val, order_rid, rowA, colA, nnzA, kWarm, kIters,
-                       tcTime),
+                    int rowA, int colA, indT nnzA, int NUM, double threshold, int block_longest, double *tcTime) {
+    check(mx_se_tcspmv(kDtype, csrValA, csrRowPtrA, csrColIdxA, X_val, Y_val, order_rid, rowA, colA, nnzA, NUM,
+                       threshold, block_longest, kWarm, kIters, tcTime),
           "se_tcspmv_fp16");
 }
 // The 8x4 / 32-bit-bitmap format of the reference's older FP16 kernels: unpacked to CSR on the host and run through the
@@ -110,9 +110,11 @@ static void du_fp16_8x4(int *chunkPtr, const std::vector<int> &fragPtr, const st
         ptr[r + 1] = (int)ind.size();
     }
     std::vector<int> order(rowA);
-    check(mx_se_tcspmv(MX_FP16, val.data(), ptr.data(), ind.data(), X_val, Y_val, order.data(), rowA, colA,
-                       (int)ind.size(), kWarm, kIters, tcTime),
+    std::vector<half> sorted(rowA);
+    check(mx_se_tcspmv(MX_FP16, val.data(), ptr.data(), ind.data(), X_val, sorted.data(), order.data(), rowA, colA,
+                       (int)ind.size(), 4, 0.75, 256, kWarm, kIters, tcTime),
           "du_tcspmv_fp16_v0/v1");
+    for (int i = 0; i < rowA; ++i) Y_val[order[i]] = sorted[i];  // results leave in the layout's row order
 }
 void du_tcspmv_fp16_v0(int *chunkPtr, std::vector<int> fragPtr, std::vector<uint32_t> fragBit, std::vector<half> tcVal,
                        int *sparse_AToX_index, half *X_val, half *Y_val, int rowA, int colA, int *, double *tcTime) {

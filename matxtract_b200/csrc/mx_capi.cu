@@ -1,5 +1,6 @@
 // C ABI of libmatxtract_b200.so: handle management, matrix upload, extraction, SpMV, timing loops, and the
 // stateless mirrors of the reference's host API (include/MatXtract.h).  See include/mx_capi.h.
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -28,13 +29,22 @@ struct mx_handle_s {
     TilePlan tile;
     ResidPlan ddcsr;         // the core-dense block as CSR, for the low-fill executor
     int dd_mode = MX_DD_AUTO;
-    bool dd_use_tile = true;
+    int dd_exec = MX_DD_TILE;  // the executor in use: MX_DD_TILE, MX_DD_CSR or MX_DD_SE
+    SePlan se;                 // sparse-encode layout of the core-dense block (built when dd_mode allows that executor)
+    int *se_col_perm[2] = {nullptr, nullptr}, *se_col_orig[2] = {nullptr, nullptr};  // slab / tail column ids
+    float dd_ms[4] = {0, 0, 0, 0};  // tuned time of the block alone, indexed by executor (0 = not timed)
+    float tuning_ms = 0;            // host time the plan-time tuners took in the last mx_partition / mx_load_partition
     // execution column space: the partition numbers columns by density rank (x must be permuted every product);
     // the same entries with their ORIGINAL column ids read x directly and keep the matrix's own locality
     int colspace_mode = MX_COLSPACE_AUTO;
     bool use_orig_cols = false;
     int *colInd_CD_orig = nullptr, *colInd_dd_orig = nullptr, *AToX_orig = nullptr;
     float tune_ms_perm = 0, tune_ms_orig = 0;
+    // hot-column prefix of the permuted x in shared memory (persistent CSR kernel)
+    int hot_mode = MX_HOT_AUTO;
+    int hot_budget = 0;       // columns that fit (0: not applicable)
+    bool use_hot = false;
+    float tune_ms_hot = 0, tune_ms_nohot = 0;
     void *ytile = nullptr;   // [n_rows] accumulate-type carrier of the tile half
     void *x_perm = nullptr;  // [n_cols] x in partition order
     // staging for the host-pointer entry point
@@ -77,12 +87,21 @@ void drop_plan(mx_handle_t h) {
     resid_plan_free(h->resid, s);
     resid_plan_free(h->ddcsr, s);
     tile_plan_free(h->tile, s);
+    if (h->se_col_perm[0]) {  // the plan owns the permuted column ids, the handle the original-numbered copies
+        h->se.slabCol = h->se_col_perm[0];
+        h->se.tailCol = h->se_col_perm[1];
+    }
+    se_plan_free(h->se, s);
+    for (int *b : h->se_col_orig)
+        if (b) cudaFreeAsync(b, s);
+    h->se_col_perm[0] = h->se_col_perm[1] = h->se_col_orig[0] = h->se_col_orig[1] = nullptr;
     part_arrays_free(h->part, s);
     void *bufs[] = {h->ytile, h->x_perm, h->colInd_CD_orig, h->colInd_dd_orig, h->AToX_orig};
     for (void *b : bufs)
         if (b) cudaFreeAsync(b, s);
     h->colInd_CD_orig = h->colInd_dd_orig = h->AToX_orig = nullptr;
-    h->use_orig_cols = false;
+    h->use_orig_cols = h->use_hot = false;
+    h->hot_budget = 0;
     h->ytile = h->x_perm = nullptr;
     h->planned = false;
     h->stats = mx_partition_stats{};
@@ -240,18 +259,26 @@ int mx_upload_csr(mx_handle_t h, int n_rows, int n_cols, int nnz, const int *row
     return MX_OK;
 }
 
-// points the execution plans at the column numbering in use
-static void select_colspace(mx_handle_t h, bool orig) {
+// points the execution plans at the column numbering in use; `hot` = serve the hot-column prefix of the permuted x
+// from shared memory (only meaningful in the permuted numbering)
+static void select_colspace(mx_handle_t h, bool orig, bool hot = false) {
     h->use_orig_cols = orig;
+    h->use_hot = !orig && hot && h->hot_budget > 0;
     h->resid.col_ind = orig ? h->colInd_CD_orig : h->part.colInd_CD;
     h->ddcsr.col_ind = orig ? h->colInd_dd_orig : h->part.colInd_dd;
     h->tile.A.AToX = orig ? h->AToX_orig : h->part.tiles.AToX;
+    if (h->se_col_perm[0]) {
+        h->se.slabCol = orig ? h->se_col_orig[0] : h->se_col_perm[0];
+        h->se.tailCol = orig ? h->se_col_orig[1] : h->se_col_perm[1];
+    }
+    h->resid.hot_cols = h->ddcsr.hot_cols = h->use_hot ? h->hot_budget : 0;
 }
 
 // the core-dense block: tensor-core tile kernel, or (low fill) the CSR kernel on the same entries
 static cudaError_t dd_enqueue(mx_handle_t h, const void *x) {
-    if (h->dd_use_tile)
+    if (h->dd_exec == MX_DD_TILE)
         return tile_spmv(h->dtype, h->tile, x, h->ytile, h->part.rId, true, false, h->dev_err, h->stream);
+    if (h->dd_exec == MX_DD_SE) return se_spmv(h->dtype, h->se, x, h->ytile, true, false, h->stream);
     return resid_spmv_to_carrier(h->dtype, h->ddcsr, x, h->ytile, h->part.rId, h->stream);
 }
 
@@ -269,7 +296,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         }
         HCK(resid_spmv_peers(h->dtype, h->resid, x, peers, n_peers, row_offset, h->stats.active ? h->ytile : nullptr,
                              h->stats.active ? h->part.hotmask : nullptr, h->stream,
-                             h->stats.active != 0 && !h->dd_use_tile, mc_y));
+                             h->stats.active != 0 && h->dd_exec == MX_DD_CSR, mc_y));
         return MX_OK;
     }
     if (h->stats.active) {
@@ -281,39 +308,51 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         if (do_tile) HCK(dd_enqueue(h, x));
         if (do_resid)
             HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->stream,
-                           /*chained=*/do_tile && !h->dd_use_tile));
+                           /*chained=*/do_tile && h->dd_exec == MX_DD_CSR));
     } else if (do_resid) {
         HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
     }
     return MX_OK;
 }
 
-// times the whole product in both column spaces on scratch vectors and keeps the faster
+// Times the whole product on scratch vectors in the candidate execution set-ups and keeps the fastest: the permuted
+// column numbering without and with the hot-column prefix in shared memory, and the original numbering.
 static int tune_colspace(mx_handle_t h) {
-    h->tune_ms_perm = h->tune_ms_orig = 0;
-    if (h->colspace_mode != MX_COLSPACE_AUTO) {
-        select_colspace(h, h->colspace_mode == MX_COLSPACE_ORIGINAL);
+    h->tune_ms_perm = h->tune_ms_orig = h->tune_ms_hot = h->tune_ms_nohot = 0;
+    const bool try_orig = h->colspace_mode != MX_COLSPACE_PERMUTED, try_perm = h->colspace_mode != MX_COLSPACE_ORIGINAL;
+    const bool try_hot = try_perm && h->hot_budget > 0 && h->hot_mode != MX_HOT_OFF;
+    const bool try_nohot = try_perm && !(try_hot && h->hot_mode == MX_HOT_ON);
+    if (!try_perm) {
+        select_colspace(h, true);
+        return MX_OK;
+    }
+    if (!try_orig && try_hot != try_nohot) {  // nothing to choose
+        select_colspace(h, false, try_hot);
         return MX_OK;
     }
     EventPair ev;
     HCK(ev.create());
-    const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
-    float ms[2] = {0, 0};
-    for (int space = 0; space < 2; ++space) {
-        select_colspace(h, space == 1);
+    auto measure = [&](bool orig, bool hot, float *ms) -> int {
+        select_colspace(h, orig, hot);
         for (int i = 0; i < 3 + 10; ++i) {
-            if (i == 3) HCK(cudaEventRecord(e0, h->stream));
+            if (i == 3) HCK(cudaEventRecord(ev.e0, h->stream));
             int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, true);
             if (st != MX_OK) return st;
         }
-        HCK(cudaEventRecord(e1, h->stream));
-        HCK(cudaEventSynchronize(e1));
-        HCK(cudaEventElapsedTime(&ms[space], e0, e1));
-    }
-    h->tune_ms_perm = ms[0] / 10;
-    h->tune_ms_orig = ms[1] / 10;
-    select_colspace(h, ms[1] < ms[0]);
+        HCK(cudaEventRecord(ev.e1, h->stream));
+        HCK(cudaEventSynchronize(ev.e1));
+        HCK(cudaEventElapsedTime(ms, ev.e0, ev.e1));
+        *ms /= 10;
+        return MX_OK;
+    };
+    int st;
+    if (try_nohot && (st = measure(false, false, &h->tune_ms_nohot)) != MX_OK) return st;
+    if (try_hot && (st = measure(false, true, &h->tune_ms_hot)) != MX_OK) return st;
+    if (try_orig && (st = measure(true, false, &h->tune_ms_orig)) != MX_OK) return st;
+    const bool hot = try_hot && (!try_nohot || h->tune_ms_hot < h->tune_ms_nohot);
+    h->tune_ms_perm = hot ? h->tune_ms_hot : h->tune_ms_nohot;
+    select_colspace(h, try_orig && h->tune_ms_orig < h->tune_ms_perm, hot);
     return MX_OK;
 }
 
@@ -321,7 +360,7 @@ static int tune_colspace(mx_handle_t h) {
 // size rule proposes a distance is timed with and without it (its half of the product alone), and the faster stays.
 static int tune_prefetch(mx_handle_t h) {
     if (getenv("MX_RESID_PREFETCH")) return MX_OK;  // forced by the environment
-    ResidPlan *plans[2] = {&h->resid, (h->stats.active && !h->dd_use_tile) ? &h->ddcsr : nullptr};
+    ResidPlan *plans[2] = {&h->resid, (h->stats.active && h->dd_exec == MX_DD_CSR) ? &h->ddcsr : nullptr};
     EventPair ev;
     for (ResidPlan *P : plans) {
         if (!P || P->prefetch_tiles <= 0 || P->num_tiles <= P->prefetch_tiles + 1) continue;
@@ -348,6 +387,51 @@ static int tune_prefetch(mx_handle_t h) {
     return MX_OK;
 }
 
+// sparse-encode layout of the core-dense block, plus its column ids in the original numbering
+static int build_se_plan(mx_handle_t h) {
+    if (h->se_col_perm[0]) return MX_OK;
+    h->se.n_rows = h->stats.dRows;
+    h->se.n_cols = h->stats.dCols;
+    h->se.nnz = h->stats.nnzRowD;
+    HCK(se_plan_build(h->dtype, h->se, h->part.rowPtr_dd, h->part.colInd_dd, h->part.val_dd, h->part.rId, h->stream));
+    h->se_col_perm[0] = h->se.slabCol;
+    h->se_col_perm[1] = h->se.tailCol;
+    const size_t slots = (size_t)h->se.numSlabs * 8 * (h->dtype == MX_FP64 ? 4 : 16);
+    HCK(cudaMallocAsync(&h->se_col_orig[0], sizeof(int) * (slots > 0 ? slots : 1), h->stream));
+    HCK(cudaMallocAsync(&h->se_col_orig[1], sizeof(int) * (size_t)(h->se.tailNnz > 0 ? h->se.tailNnz : 1), h->stream));
+    HCK(map_indices(h->se_col_perm[0], h->part.xperm, h->se_col_orig[0], (long long)slots, h->stream));
+    HCK(map_indices(h->se_col_perm[1], h->part.xperm, h->se_col_orig[1], h->se.tailNnz, h->stream));
+    return MX_OK;
+}
+
+// MX_DD_AUTO: the core-dense block alone is timed through each of its three executors (tensor-core fragments,
+// CUDA-core CSR, tensor-core sparse-encode) on the device and the fastest is kept.  The reference decides from two
+// fixed thresholds tuned on another GPU (test/test_autotc_spmv.cpp:1507,1518).
+static int tune_dd_executor(mx_handle_t h) {
+    h->dd_ms[MX_DD_TILE] = h->dd_ms[MX_DD_CSR] = h->dd_ms[MX_DD_SE] = 0;
+    if (h->dd_mode != MX_DD_AUTO || !h->stats.active) return MX_OK;
+    EventPair ev;
+    HCK(ev.create());
+    HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
+    int best = MX_DD_CSR;
+    for (int ex : {MX_DD_TILE, MX_DD_CSR, MX_DD_SE}) {
+        h->dd_exec = ex;
+        for (int i = 0; i < 2 + 6; ++i) {
+            if (i == 2) HCK(cudaEventRecord(ev.e0, h->stream));
+            int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, false, /*permute=*/i == 0);
+            if (st != MX_OK) return st;
+        }
+        HCK(cudaEventRecord(ev.e1, h->stream));
+        HCK(cudaEventSynchronize(ev.e1));
+        float ms = 0;
+        HCK(cudaEventElapsedTime(&ms, ev.e0, ev.e1));
+        h->dd_ms[ex] = ms / 6;
+        if (ex == MX_DD_TILE || h->dd_ms[ex] < h->dd_ms[best]) best = ex;
+    }
+    h->dd_exec = best;
+    return MX_OK;
+}
+
 // Everything that follows the extraction proper (or the loading of a stored partition): execution plans of the two
 // halves, the carrier, the index arrays in original column numbering, and the choice of the execution column space.
 static int finish_partition(mx_handle_t h) {
@@ -367,8 +451,14 @@ static int finish_partition(mx_handle_t h) {
     h->ddcsr.col_ind = h->part.colInd_dd;
     h->ddcsr.val = h->part.val_dd;
     HCK(resid_plan_build(h->dtype, h->ddcsr, h->stream));
-    h->dd_use_tile = h->dd_mode == MX_DD_TILE ||
-                     (h->dd_mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
+    h->resid.dev_err = h->ddcsr.dev_err = h->dev_err;
+    h->hot_budget = resid_hot_cols_budget(h->dtype, h->stats.dCols);
+    if (h->dd_mode == MX_DD_AUTO || h->dd_mode == MX_DD_SE) {
+        int sst = build_se_plan(h);
+        if (sst != MX_OK) return sst;
+    }
+    h->dd_exec = h->dd_mode == MX_DD_AUTO ? (h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL ? MX_DD_TILE : MX_DD_CSR)
+                                          : h->dd_mode;
     HCK(cudaMallocAsync(&h->ytile, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
     HCK(cudaMemsetAsync(h->ytile, 0, acc_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
     HCK(cudaMallocAsync(&h->x_perm, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
@@ -380,13 +470,17 @@ static int finish_partition(mx_handle_t h) {
     HCK(map_indices(h->part.colInd_CD, h->part.xperm, h->colInd_CD_orig, h->stats.nnzCD, h->stream));
     HCK(map_indices(h->part.colInd_dd, h->part.xperm, h->colInd_dd_orig, h->stats.nnzRowD, h->stream));
     HCK(map_indices(h->part.tiles.AToX, h->part.xperm, h->AToX_orig, (long long)nAToX, h->stream));
-    h->planned = true;  // the tuner runs real products
-    int tst = tune_colspace(h);
+    h->planned = true;  // the tuners run real products
+    const auto t0 = std::chrono::steady_clock::now();
+    select_colspace(h, false);
+    int tst = tune_dd_executor(h);
+    if (tst == MX_OK) tst = tune_colspace(h);
     if (tst == MX_OK) tst = tune_prefetch(h);
     if (tst != MX_OK) {
         drop_plan(h);
         return tst;
     }
+    h->tuning_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return MX_OK;
 }
 
@@ -396,6 +490,7 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
     if (tau_c < tau_r) return h->fail(MX_ERR_TAU, "col_frac must be greater than hot_frac");
     HCK(cudaSetDevice(h->device));
     drop_plan(h);
+    h->tuning_ms = 0;
     const float colProp = (float)tau_c, rowProp = (float)tau_r;
     EventPair ev;
     HCK(ev.create());
@@ -417,11 +512,13 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         h->stats.sRows = h->n_rows;
         h->stats.nnzColS = h->nnz;
         h->planned = true;  // the tuner runs real products
+        const auto t0 = std::chrono::steady_clock::now();
         int tst = tune_prefetch(h);
         if (tst != MX_OK) {
             drop_plan(h);
             return tst;
         }
+        h->tuning_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     } else {
         // The reference assumes a square matrix (its tau_c scan runs i < rowA over the column table,
         // test/test_autotc_spmv.cpp:1133).  A rectangular row slab (one GPU's share of a row-partitioned
@@ -451,7 +548,9 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
     HCK(cudaEventSynchronize(e1));
     float ms = 0;
     HCK(cudaEventElapsedTime(&ms, e0, e1));
-    h->stats.preprocess_ms = ms;
+    // the tuners' timed products are reported on their own, not as extraction time
+    h->stats.tuning_ms = h->tuning_ms;
+    h->stats.preprocess_ms = ms > h->tuning_ms ? ms - h->tuning_ms : ms;
     h->planned = true;
     if (stats) *stats = h->stats;
     return MX_OK;
@@ -562,6 +661,7 @@ int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats
     int st = finish_partition(h);
     if (st != MX_OK) return refuse(st);
     HCK(cudaStreamSynchronize(h->stream));
+    h->stats.tuning_ms = h->tuning_ms;
     if (stats) *stats = h->stats;
     return MX_OK;
 }
@@ -703,15 +803,34 @@ int mx_spmv_launches(mx_handle_t h) {
     if (!h || !h->planned) return 0;
     int n = resid_launches(h->resid);
     if (h->stats.active)
-        n += (h->use_orig_cols ? 0 : 1) + (h->dd_use_tile ? tile_launches(h->tile) : resid_launches(h->ddcsr));
+        n += (h->use_orig_cols ? 0 : 1) + (h->dd_exec == MX_DD_TILE ? tile_launches(h->tile)
+                                         : h->dd_exec == MX_DD_SE ? se_launches(h->se)
+                                                                  : resid_launches(h->ddcsr));
     return n;
 }
 
 int mx_set_dd_executor(mx_handle_t h, int mode) {
-    if (!h || mode < MX_DD_AUTO || mode > MX_DD_CSR) return MX_ERR_INVALID;
+    if (!h || mode < MX_DD_AUTO || mode > MX_DD_SE) return MX_ERR_INVALID;
     h->dd_mode = mode;
-    if (h->planned && h->stats.active)
-        h->dd_use_tile = mode == MX_DD_TILE || (mode == MX_DD_AUTO && h->stats.tc_nnz_ratio >= MX_DD_AUTO_FILL);
+    if (h->planned && h->stats.active) {
+        HCK(cudaSetDevice(h->device));
+        HCK(cudaStreamSynchronize(h->stream));
+        if (mode == MX_DD_AUTO || mode == MX_DD_SE) {
+            int st = build_se_plan(h);
+            if (st != MX_OK) return st;
+            select_colspace(h, h->use_orig_cols, h->use_hot);
+        }
+        if (mode == MX_DD_AUTO) return tune_dd_executor(h);
+        h->dd_exec = mode;
+    }
+    return MX_OK;
+}
+
+int mx_dd_executor_times(mx_handle_t h, float *ms_tile, float *ms_csr, float *ms_se) {
+    if (!h) return MX_ERR_INVALID;
+    if (ms_tile) *ms_tile = h->dd_ms[MX_DD_TILE];
+    if (ms_csr) *ms_csr = h->dd_ms[MX_DD_CSR];
+    if (ms_se) *ms_se = h->dd_ms[MX_DD_SE];
     return MX_OK;
 }
 
@@ -726,6 +845,26 @@ int mx_set_column_space(mx_handle_t h, int mode) {
     return MX_OK;
 }
 
+int mx_set_hot_prefix(mx_handle_t h, int mode) {
+    if (!h || mode < MX_HOT_AUTO || mode > MX_HOT_ON) return MX_ERR_INVALID;
+    h->hot_mode = mode;
+    if (h->planned && h->stats.active) {
+        HCK(cudaSetDevice(h->device));
+        HCK(cudaStreamSynchronize(h->stream));
+        return tune_colspace(h);
+    }
+    return MX_OK;
+}
+
+int mx_hot_prefix(mx_handle_t h, int *hot_cols, float *ms_with, float *ms_without) {
+    if (!h) return MX_ERR_INVALID;
+    const bool on = h->planned && h->stats.active && h->use_hot;
+    if (hot_cols) *hot_cols = on ? h->hot_budget : 0;
+    if (ms_with) *ms_with = h->tune_ms_hot;
+    if (ms_without) *ms_without = h->tune_ms_nohot;
+    return MX_OK;
+}
+
 int mx_column_space(mx_handle_t h, float *ms_permuted, float *ms_original) {
     if (!h || !h->planned || !h->stats.active) return MX_COLSPACE_AUTO;
     if (ms_permuted) *ms_permuted = h->tune_ms_perm;
@@ -735,7 +874,7 @@ int mx_column_space(mx_handle_t h, float *ms_permuted, float *ms_original) {
 
 int mx_dd_executor(mx_handle_t h) {
     if (!h || !h->planned || !h->stats.active) return MX_DD_AUTO;
-    return h->dd_use_tile ? MX_DD_TILE : MX_DD_CSR;
+    return h->dd_exec;
 }
 
 int mx_device_error(mx_handle_t h, int *err) {
@@ -958,7 +1097,8 @@ int mx_du_tcspmv(int dtype, const int *chunkPtr, const int *fragPtr, const void 
 }
 
 int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int *csrColIdx, const void *x, void *y,
-                 int *order_rid, int rowA, int colA, int nnzA, int warm, int iters, double *ms_per_spmv) {
+                 int *order_rid, int rowA, int colA, int nnzA, int NUM, double threshold, int block_longest, int warm,
+                 int iters, double *ms_per_spmv) {
     if ((dtype != MX_FP64 && dtype != MX_FP16) || !csrRowPtr || !x || !y || !order_rid || rowA < 0 || colA < 0 ||
         nnzA < 0 || (nnzA > 0 && (!csrVal || !csrColIdx)))
         return MX_ERR_INVALID;
@@ -967,27 +1107,41 @@ int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int 
     const size_t vb = val_bytes(dtype);
     DevBufs B;
     int *d_ptr, *d_ind;
-    void *d_val, *d_x, *d_y, *d_scratch;
+    void *d_val, *d_x, *d_y;
     SCK(B.up(&d_ptr, csrRowPtr, sizeof(int) * ((size_t)rowA + 1)));
     SCK(B.up(&d_ind, csrColIdx, sizeof(int) * (size_t)nnzA));
     SCK(B.up(&d_val, csrVal, vb * (size_t)nnzA));
     SCK(B.up(&d_x, x, vb * (size_t)colA));
     SCK(B.up(&d_y, nullptr, vb * (size_t)rowA));
-    SCK(B.up(&d_scratch, nullptr, vb * (size_t)rowA));
-    TileArrays T;
-    int tstatus = MX_OK;
-    cudaError_t ce = tiles_from_dd(dtype, rowA, nnzA, d_ptr, d_ind, d_val, T, &tstatus, 0);
-    T.dCols = colA;
-    if (ce == cudaSuccess && tstatus == MX_OK) {
-        st = run_tiles(dtype, T, d_x, d_y, d_scratch, warm, iters, false, ms_per_spmv);
-        if (st == MX_OK && cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost) != cudaSuccess)
-            st = MX_ERR_CUDA;
-    } else {
-        st = ce != cudaSuccess ? MX_ERR_CUDA : tstatus;
+    SePlan P;
+    P.n_rows = rowA;
+    P.n_cols = colA;
+    P.nnz = nnzA;
+    if (NUM > 0) P.warps_per_cta = NUM;
+    if (threshold >= 0.0) P.threshold = threshold;
+    if (block_longest > 0) P.block_longest = block_longest;
+    cudaError_t ce = se_plan_build(dtype, P, d_ptr, d_ind, d_val, nullptr, 0);
+    EventPair ev;
+    if (ce == cudaSuccess) ce = ev.create();
+    for (int i = 0; i < warm + iters && ce == cudaSuccess; ++i) {
+        if (i == warm) cudaEventRecord(ev.e0, 0);
+        ce = se_spmv(dtype, P, d_x, d_y, false, false, 0);
     }
-    tile_arrays_free(T, 0);
-    for (int i = 0; i < rowA; ++i) order_rid[i] = i;
-    return st;
+    if (iters > 0 && ce == cudaSuccess) {
+        cudaEventRecord(ev.e1, 0);
+        cudaEventSynchronize(ev.e1);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ev.e0, ev.e1);
+        if (ms_per_spmv) *ms_per_spmv = ms / iters;
+    }
+    // Y_val[i] is the result of input row order_rid[i]: rows leave in the layout's length-sorted order
+    if (ce == cudaSuccess) ce = se_spmv(dtype, P, d_x, d_y, false, false, 0);
+    if (ce == cudaSuccess && rowA > 0) ce = cudaMemcpy(y, d_y, vb * (size_t)rowA, cudaMemcpyDeviceToHost);
+    if (ce == cudaSuccess && rowA > 0) ce = cudaMemcpy(order_rid, P.order, sizeof(int) * (size_t)rowA, cudaMemcpyDeviceToHost);
+    se_plan_free(P, 0);
+    cudaDeviceSynchronize();
+    SCK(ce);
+    return MX_OK;
 }
 
 }  // extern "C"

@@ -53,6 +53,9 @@ struct ResidPlan {
     const void *val = nullptr;     // [nnz]
     int tile_nnz = 0, num_tiles = 0;
     int prefetch_tiles = 0;          // L2 prefetch distance of the CSR kernel in tiles (0: off)
+    int hot_cols = 0;                // > 0: x[0, hot_cols) is the hot-column prefix of a permuted x; the persistent kernel
+                                     // keeps it in shared memory (a multiple of 16 bytes of values)
+    int *dev_err = nullptr;          // device error word for bounded waits (may be null)
     int m_rows = 0, n_empty = 0;     // non-empty / empty rows
     const int *c_ptr = nullptr;      // [m_rows+1] row pointers of the non-empty rows (= row_ptr when none is empty)
     int *c_ptr_own = nullptr;        // storage of c_ptr when it is not row_ptr
@@ -99,6 +102,29 @@ struct TilePlan {
     void *segDesc = nullptr;          // [numSegs] packed {panel, first fragment, end fragment, slot}
 };
 
+// Sparse-encode layout of a CSR block (se_spmv.cu): rows sorted by length, 8-row blocks of zero-padded 8xK slabs for
+// the tensor cores, irregular tails as CSR.  Owned.
+struct SePlan {
+    int n_rows = 0, n_cols = 0, nnz = 0;
+    // the reference's tuning knobs (test/test_autotc_spmv.cpp:1501-1503): warps per CTA, the fill a slab needs to be
+    // stored for the tensor cores, and the length from which a row is "long"
+    int warps_per_cta = 4;
+    double threshold = 0.75;
+    int block_longest = 256;
+    int nLong = 0, numBlocks = 0, numSlabs = 0, numUnits = 0, tailNnz = 0;
+    int *order = nullptr;     // [n_rows] sorted position -> input row
+    int *outRow = nullptr;    // [n_rows] sorted position -> index the row's result is written to
+    int *slabPtr = nullptr;   // [numBlocks+1]
+    int *unitPtr = nullptr;   // [numBlocks+1] work units (<= 64 slabs each) of every block
+    void *unitDesc = nullptr; // [numUnits] int4 {block, first slab, end slab, 0}
+    void *slabVal = nullptr;  // [numSlabs * 8K] values in MMA operand order
+    int *slabCol = nullptr;   // [numSlabs * 8K] their column ids
+    int *tailPtr = nullptr;   // [n_rows+1] irregular tails, by sorted position
+    void *tailVal = nullptr;
+    int *tailCol = nullptr;
+    void *partial = nullptr;  // [numUnits][8] accumulate-type diagonal sums
+};
+
 // Everything the extraction produces, on the device (owned).
 struct PartArrays {
     int *xperm = nullptr;        // [n_cols]
@@ -130,6 +156,9 @@ cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, vo
                              long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
                              bool chained = false, void *mc_y = nullptr);
 int resid_launches(const ResidPlan &plan);
+// largest hot-column prefix (columns, rounded down to 16 bytes of values) the persistent CSR kernel can hold in shared
+// memory for this value type; 0 when `d_cols` is too small to be worth a persistent launch
+int resid_hot_cols_budget(int dtype, int d_cols);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
 void tile_plan_free(TilePlan &plan, cudaStream_t s);
@@ -137,6 +166,16 @@ void tile_plan_free(TilePlan &plan, cudaStream_t s);
 cudaError_t tile_spmv(int dtype, const TilePlan &plan, const void *x_d, void *out, const int *row_map,
                       bool out_is_acc, bool accumulate, int *dev_err, cudaStream_t s);
 int tile_launches(const TilePlan &plan);
+
+// Builds the sparse-encode layout of the CSR block (rowPtr, colInd, val) with P.n_rows / n_cols / nnz and the knobs
+// set; row_map (may be null) sends the result of input row i to out[row_map[i]] instead of its sorted position.
+cudaError_t se_plan_build(int dtype, SePlan &P, const int *rowPtr, const int *colInd, const void *val,
+                          const int *row_map, cudaStream_t s);
+void se_plan_free(SePlan &P, cudaStream_t s);
+// out[outRow[r]] (accumulate type when out_is_acc, else value type) = result of sorted row r
+cudaError_t se_spmv(int dtype, const SePlan &P, const void *x, void *out, bool out_is_acc, bool accumulate,
+                    cudaStream_t s);
+int se_launches(const SePlan &P);
 
 cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st,
                           int *status, cudaStream_t s);

@@ -120,30 +120,6 @@ struct CtaDesc {  // computed at plan time
     int pad0, pad1;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// waits for phase 0 of the barrier; gives up after a bounded number of polls (returns false)
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar) {
-    const uint32_t a = smem_u32(bar);
-    for (int it = 0; it < (1 << 22); ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(a), "r"(0u)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
 constexpr int STAGE_WARPS = 4;   // warps per CTA (8 measured slower)
 int g_tile_prefetch = -1;        // L2 prefetch distance in CTAs; default 5 per SM (A/B on the block matrix: tile half
                                  // 113.8 -> 108.7 us; 10 per SM 110.1, 20 per SM 122.8), MX_TILE_PREFETCH overrides, 0 = off

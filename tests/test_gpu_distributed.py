@@ -20,7 +20,8 @@ import oracle
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
-for name, n, tau in (("c2", 60000, (0.46, 0.33)), ("c3", 8 * 4000, (0.5, 0.5)), ("c5", 50000, (0.0, 0.0))):
+for name, n, tau in (("c2", 60000, (0.46, 0.33)), ("c3", 8 * 4000, (0.5, 0.5)), ("c5", 50000, (0.0, 0.0)),
+                     ("c4", 60000, (0.5, 0.25))):
     m = synth.generate(name, n=n)
     dtype = m["dtype"]
     d = D.DistributedSpMV(dtype, n, m["row_ptr"], m["col_ind"], m["val"], rank, world, tau=tau)
@@ -72,4 +73,4 @@ def test_two_rank_row_partition_matches_the_oracle(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), str(ROOT)],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count(" ok ") == 6
+    assert r.stdout.count(" ok ") == 8

@@ -9,7 +9,7 @@ import matxtract_b200 as mx
 import oracle
 from matxtract_b200 import FP16, FP64, synth
 
-from cases import TAUS, small_cases, values
+from cases import TAUS, random_csr, small_cases, values
 
 pytestmark = pytest.mark.gpu
 
@@ -327,4 +327,84 @@ def test_stream_gather_floor_is_measured_below_the_product():
     assert 0 < floor < t * 1.5   # no row logic, nothing written: cannot be much slower than the real product
     torch.cuda.synchronize()
     del x_dev, y_dev
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+@pytest.mark.parametrize("dd", [mx.DD_CSR, mx.DD_TILE])
+def test_hot_column_prefix_in_shared_memory_gives_the_same_bits(dtype, dd):
+    """The persistent CSR kernel that serves the hot-column prefix of x from shared memory does the same arithmetic in
+    the same order as the one-tile-per-CTA kernel: identical y bits, partition arrays untouched."""
+    m = synth.generate("c4", n=60_000, dtype=dtype)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, val)
+    for tau in ((0.5, 0.25), (0.4, 0.0), (0.9, 0.9)):
+        st = h.partition(*tau)
+        h.set_dd_executor(dd)
+        h.set_column_space(mx.COLSPACE_PERMUTED)
+        h.set_hot_prefix(mx.HOT_OFF)
+        assert h.hot_prefix[0] == 0
+        y_off = h.spmv_host(x)
+        before = h.download_partition()
+        h.set_hot_prefix(mx.HOT_ON)
+        cols = h.hot_prefix[0]
+        assert 0 < cols <= st.dCols and (cols * (8 if dtype == FP64 else 2)) % 16 == 0
+        y_on = h.spmv_host(x)
+        np.testing.assert_array_equal(_bits(y_on), _bits(y_off))
+        check_y(dtype, y_on, rp, ci, val, x)
+        after = h.download_partition()
+        for k in PART_KEYS:
+            np.testing.assert_array_equal(_bits(before[k]), _bits(after[k]), err_msg=k)
+        assert h.device_error() == 0
+        h.set_hot_prefix(mx.HOT_AUTO)
+    h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_sparse_encode_entry_point_honours_its_knobs(dtype):
+    """mx_se_tcspmv builds the sparse-encode layout on the device: any NUM / threshold / block_longest gives the same
+    product (within tolerance), returned in length-sorted row order with the permutation in order_rid."""
+    rp, ci = random_csr(700, 9, 21, empty_rows=0.15, skew=True)   # empty rows, rows of 1-4, a few very long rows
+    val = values(dtype, len(ci), 21)
+    x = values(dtype, 700, 22)
+    want = oracle.exact_spmv(rp, ci, val, x)
+    scale = oracle.abs_rowsum_max(dtype, rp, ci, val, x)
+    lens = np.diff(rp)
+    for num, thr, longest in ((4, 0.75, 256), (1, 0.0, 8), (8, 1.0, 16), (3, 0.5, 40), (0, -1.0, 0)):
+        y_se, order, _ = mx.se_tcspmv(dtype, val, rp, ci, x, warm=0, iters=1, num=num, threshold=thr,
+                                      block_longest=longest)
+        assert sorted(order.tolist()) == list(range(700))
+        assert (np.diff(lens[order]) <= 0).all()  # longest rows first
+        got = np.empty_like(y_se)
+        got[order] = y_se
+        err = np.abs(got.astype(np.float64) - want).max() / scale
+        assert err <= (1e-13 if dtype == FP64 else 6e-4), (num, thr, longest, err)
+
+
+@pytest.mark.parametrize("name,n,tau", [("c2", 200_000, (0.46, 0.33)), ("c4", 300_000, (0.5, 0.25)),
+                                        ("c3", 8 * 30_000, (0.5, 0.5)), ("c5", 400_000, (0.7, 0.5))])
+def test_core_dense_block_through_each_executor(name, n, tau):
+    """tile / csr / sparse-encode executors of the core-dense block give the same y within tolerance, leave the
+    partition arrays alone, and the automatic choice reports a time for each."""
+    m = synth.generate(name, n=n)
+    dtype, rp, ci, val, x = m["dtype"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(dtype)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(*tau)
+    t_tile, t_csr, t_se = h.dd_executor_times
+    assert min(t_tile, t_csr, t_se) > 0
+    fastest = min(((t_tile, mx.DD_TILE), (t_csr, mx.DD_CSR), (t_se, mx.DD_SE)))[0]
+    assert {mx.DD_TILE: t_tile, mx.DD_CSR: t_csr, mx.DD_SE: t_se}[h.dd_executor] == fastest
+    before = h.download_partition()
+    for ex in (mx.DD_TILE, mx.DD_CSR, mx.DD_SE):
+        h.set_dd_executor(ex)
+        assert h.dd_executor == ex
+        for space in (mx.COLSPACE_PERMUTED, mx.COLSPACE_ORIGINAL):
+            h.set_column_space(space)
+            check_y(dtype, h.spmv_host(x), rp, ci, val, x)
+    after = h.download_partition()
+    for k in PART_KEYS:
+        np.testing.assert_array_equal(_bits(before[k]), _bits(after[k]), err_msg=k)
+    assert h.device_error() == 0
     h.close()
