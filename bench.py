@@ -396,6 +396,9 @@ def run_ours(args):
         h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR, "se": mx.DD_SE}[args.dd])
     if args.colspace != "auto":
         h.set_column_space({"permuted": mx.COLSPACE_PERMUTED, "original": mx.COLSPACE_ORIGINAL}[args.colspace])
+    if args.colslabs != -1:
+        h.set_column_slabs(args.colslabs)
+    slabs = h.column_slabs
     if args.hotx != "auto":
         h.set_hot_prefix({"off": mx.HOT_OFF, "on": mx.HOT_ON}[args.hotx])
     colspace = h.column_space
@@ -624,6 +627,8 @@ def run_ours(args):
         dom, dom_ms, dom_bytes = dd_names.get(h.dd_executor, "dd"), halves["ms_tile"], b_dd
     else:
         dom, dom_ms, dom_bytes = "resid_kernel(+fixup)", halves["ms_resid"], b_resid
+        if slabs[0] > 0:
+            dom = f"resid_kernel(+fixup) in {slabs[0]} column-slab passes"
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     traffic, traffic_note = (profiled_traffic(cfg.name, dom, tau, n_total) if world == 1 else (None, "N > 1: not captured"))
     eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
@@ -702,11 +707,13 @@ def run_ours(args):
         "dd_executor_tuned_ms": {"tile": dd_times[0], "csr": dd_times[1], "sparse_encode": dd_times[2]},
         "column_space": {"in_use": {1: "permuted", 2: "original"}.get(colspace[0], "n/a"),
                          "tuned_ms_permuted": colspace[1], "tuned_ms_original": colspace[2]},
+        "column_slabs": {"in_use": slabs[0], "tuned_ms_plain": slabs[1], "tuned_ms_slabbed": slabs[2]},
         "hot_x_prefix": {"columns_in_shared_memory": hot[0], "tuned_ms_with": hot[1], "tuned_ms_without": hot[2]},
         "csr_l2_prefetch_tiles": {"resid": h.csr_prefetch[0], "dd": h.csr_prefetch[1]},
         "tc_nnz_ratio": st.tc_nnz_ratio, "preprocess_ms": st.preprocess_ms, "preprocess_ms_first_call": preprocess_ms_cold,
         "plan_tuning_ms": st.tuning_ms,
         "ms_dd_alone": halves["ms_tile"], "ms_resid_alone": halves["ms_resid"], "ms_sequence": halves["ms_total"],
+        "launches_per_spmv": h.launches_per_spmv,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "traffic_note": traffic_note,
                      "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
@@ -748,6 +755,8 @@ def main():
                     help="executor of the core-dense block (auto = the fastest of the three, timed at partition time)")
     ap.add_argument("--colspace", default="auto", choices=["auto", "permuted", "original"],
                     help="column numbering used for execution")
+    ap.add_argument("--colslabs", type=int, default=-1,
+                    help="column slabs of the plain CSR product: -1 auto (when x exceeds L2), 0 off, k >= 2 forced")
     ap.add_argument("--hotx", default="auto", choices=["auto", "on", "off"],
                     help="hot-column prefix of x in shared memory (permuted numbering only)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU baseline leg (profiling runs)")

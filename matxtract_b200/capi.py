@@ -93,6 +93,8 @@ SYMBOLS = {
     "mx_dd_executor": (_i, [_vp]),
     "mx_set_column_space": (_i, [_vp, _i]),
     "mx_column_space": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mx_set_column_slabs": (_i, [_vp, _i]),
+    "mx_column_slabs": (_i, [_vp, _ip, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_set_hot_prefix": (_i, [_vp, _i]),
     "mx_hot_prefix": (_i, [_vp, _ip, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_device_error": (_i, [_vp, _ip]),
@@ -303,6 +305,17 @@ class MatXtract:
         a, b = C.c_float(), C.c_float()
         m = lib().mx_column_space(self._h, C.byref(a), C.byref(b))
         return m, a.value, b.value
+
+    def set_column_slabs(self, count: int):
+        """-1 = automatic (when x exceeds L2, timed), 0 = off, k >= 2 = k column slabs (tau = (0,0), FP64)."""
+        self._ck(lib().mx_set_column_slabs(self._h, count))
+
+    @property
+    def column_slabs(self):
+        """(slabs in use, 0 = plain kernel; ms per product plain; ms per product slabbed) of the last choice."""
+        n, a, b = C.c_int(), C.c_float(), C.c_float()
+        self._ck(lib().mx_column_slabs(self._h, C.byref(n), C.byref(a), C.byref(b)))
+        return n.value, a.value, b.value
 
     def set_hot_prefix(self, mode: int):
         """0 = auto (timed at partition time), 1 = off, 2 = on: hot-column prefix of x in shared memory."""

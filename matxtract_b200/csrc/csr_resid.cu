@@ -783,6 +783,20 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &P, cudaStream_t s) {
                                                                     P.empty_row);
         P.c_ptr = P.c_ptr_own;
     }
+    e = resid_plan_finish(dtype, P, s);
+    if (flag) cudaFreeAsync(flag, s);
+    if (pos) cudaFreeAsync(pos, s);
+    return e;
+}
+
+// The part of the plan that follows the row compression: per-tile row offsets and the carry / head slots.  Callers
+// that already hold the compressed row table (c_ptr, nz_row, m_rows, n_empty) of a matrix call this directly.
+cudaError_t resid_plan_finish(int dtype, ResidPlan &P, cudaStream_t s) {
+    cudaError_t e;
+    if (P.tile_nnz == 0) {
+        P.tile_nnz = RESID_THREADS * (dtype == MX_FP64 ? ResidCfg<double>::IPT : ResidCfg<__half>::IPT);
+        P.num_tiles = P.nnz > 0 ? (int)(((long long)P.nnz + P.tile_nnz - 1) / P.tile_nnz) : 1;
+    }
     if ((e = cudaMallocAsync(&P.tile_row, sizeof(int) * (size_t)(P.num_tiles + 1), s)) != cudaSuccess) return e;
     if ((e = cudaMallocAsync(&P.carry, acc_bytes(dtype) * (size_t)P.num_tiles, s)) != cudaSuccess) return e;
     if ((e = cudaMallocAsync(&P.head, acc_bytes(dtype) * (size_t)P.num_tiles, s)) != cudaSuccess) return e;
@@ -790,8 +804,6 @@ cudaError_t resid_plan_build(int dtype, ResidPlan &P, cudaStream_t s) {
                                                                   P.tile_row);
     e = cudaGetLastError();
     cudaError_t e2 = cudaStreamSynchronize(s);
-    if (flag) cudaFreeAsync(flag, s);
-    if (pos) cudaFreeAsync(pos, s);
     return e != cudaSuccess ? e : e2;
 }
 

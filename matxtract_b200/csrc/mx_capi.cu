@@ -34,6 +34,12 @@ struct mx_handle_s {
     int *se_col_perm[2] = {nullptr, nullptr}, *se_col_orig[2] = {nullptr, nullptr};  // slab / tail column ids
     float dd_ms[4] = {0, 0, 0, 0};  // tuned time of the block alone, indexed by executor (0 = not timed)
     float tuning_ms = 0;            // host time the plan-time tuners took in the last mx_partition / mx_load_partition
+    // column-slab execution of the plain CSR product (tau = (0,0)) when x is far larger than L2
+    int slab_mode = -1;             // -1 = automatic, 0 = off, k >= 2 = k slabs
+    ColSlabs slabs;
+    bool use_slabs = false;
+    float slab_ms_plain = 0, slab_ms_slabbed = 0;
+    void *peer_table = nullptr;     // 64 bytes: peer row addresses for the slab path's push
     // execution column space: the partition numbers columns by density rank (x must be permuted every product);
     // the same entries with their ORIGINAL column ids read x directly and keep the matrix's own locality
     int colspace_mode = MX_COLSPACE_AUTO;
@@ -86,6 +92,8 @@ void drop_plan(mx_handle_t h) {
     cudaStream_t s = h->stream;  // frees are ordered after whatever the stream still has in flight
     resid_plan_free(h->resid, s);
     resid_plan_free(h->ddcsr, s);
+    col_slabs_free(h->slabs, s);
+    h->use_slabs = false;
     tile_plan_free(h->tile, s);
     if (h->se_col_perm[0]) {  // the plan owns the permuted column ids, the handle the original-numbered copies
         h->se.slabCol = h->se_col_perm[0];
@@ -190,7 +198,8 @@ int mx_create(mx_handle_t *out, int device, int dtype) {
     h->device = device;
     h->dtype = dtype;
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaMalloc(&h->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(h->dev_err, 0, sizeof(int)) != cudaSuccess) {
+        cudaMalloc(&h->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(h->dev_err, 0, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&h->peer_table, 64) != cudaSuccess) {
         delete h;
         return MX_ERR_CUDA;
     }
@@ -205,6 +214,7 @@ int mx_destroy(mx_handle_t h) {
     drop_matrix(h);
     cudaStreamSynchronize(h->stream);
     cudaFree(h->dev_err);
+    cudaFree(h->peer_table);
     cudaStreamDestroy(h->stream);
     delete h;
     return MX_OK;
@@ -285,6 +295,23 @@ static cudaError_t dd_enqueue(mx_handle_t h, const void *x) {
 static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_tile, bool do_resid,
                         bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0,
                         void *mc_y = nullptr) {
+    if (peers && h->use_slabs && !h->stats.active) {
+        // column-slab passes accumulate into this GPU's own rows of its own y; the finished rows are then pushed
+        int self = -1;
+        for (int g = 0; g < n_peers && self < 0; ++g) {
+            cudaPointerAttributes at{};
+            if (cudaPointerGetAttributes(&at, peers[g]) == cudaSuccess && at.device == h->device &&
+                at.type == cudaMemoryTypeDevice)
+                self = g;
+        }
+        cudaGetLastError();
+        if (self < 0) return h->fail(MX_ERR_INVALID, "mx_spmv_peers: none of the buffers lives on this handle's GPU");
+        const size_t vb = val_bytes(h->dtype);
+        void *y_own = static_cast<char *>(peers[self]) + (size_t)row_offset * vb;
+        HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, h->stream));
+        int pst = mx_peer_push(h->dtype, peers, n_peers, self, row_offset, h->n_rows, h->peer_table, h->stream);
+        return pst == MX_OK ? MX_OK : h->fail(pst, "mx_spmv_peers: peer push failed");
+    }
     if (peers) {  // final rows go to every GPU's y
         const void *x = x_dev;
         if (h->stats.active) {
@@ -310,7 +337,10 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
             HCK(resid_spmv(h->dtype, h->resid, x, y_dev, h->ytile, h->part.hotmask, false, h->stream,
                            /*chained=*/do_tile && h->dd_exec == MX_DD_CSR));
     } else if (do_resid) {
-        HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
+        if (h->use_slabs)
+            HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_dev, val_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
+        else
+            HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
     }
     return MX_OK;
 }
@@ -384,6 +414,54 @@ static int tune_prefetch(mx_handle_t h) {
         }
         P->prefetch_tiles = ms[0] <= ms[1] ? cand[0] : 0;
     }
+    return MX_OK;
+}
+
+// Plain CSR product (tau = (0,0)) of a matrix whose x is far larger than L2: build the column slabs, time the product
+// both ways on scratch vectors and keep the faster.  FP64 only (the passes add into y in the value type).
+static int tune_col_slabs(mx_handle_t h) {
+    h->use_slabs = false;
+    h->slab_ms_plain = h->slab_ms_slabbed = 0;
+    if (h->dtype != MX_FP64 || h->slab_mode == 0 || h->stats.active || h->nnz <= 0) return MX_OK;
+    int l2 = 0;
+    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->device);
+    const size_t xbytes = val_bytes(h->dtype) * (size_t)h->n_cols;
+    constexpr size_t SLAB_X_BYTES = 32u << 20;  // the x range of one pass
+    int count = h->slab_mode;
+    if (count < 0) {
+        if (l2 <= 0 || xbytes <= (size_t)l2) return MX_OK;  // x fits L2: nothing to gain
+        count = (int)std::min<size_t>(64, (xbytes + SLAB_X_BYTES - 1) / SLAB_X_BYTES);
+    }
+    if (count < 2) return MX_OK;
+    CsrDev A;
+    A.n_rows = h->n_rows, A.n_cols = h->n_cols, A.nnz = h->nnz;
+    A.row_ptr = h->row_ptr, A.col_ind = h->col_ind, A.val = h->val;
+    int status = MX_OK;
+    HCK(col_slabs_build(h->dtype, A, count, h->slabs, &status, h->stream));
+    if (status != MX_OK) return MX_OK;  // rows not sorted by column: the plain kernel stays
+    if (h->slab_mode > 0) {
+        h->use_slabs = true;
+        return MX_OK;
+    }
+    EventPair ev;
+    HCK(ev.create());
+    HCK(cudaMemsetAsync(h->x_stage, 0, xbytes, h->stream));
+    float ms[2] = {0, 0};
+    for (int v = 0; v < 2; ++v) {
+        h->use_slabs = v == 1;
+        for (int i = 0; i < 2 + 5; ++i) {
+            if (i == 2) HCK(cudaEventRecord(ev.e0, h->stream));
+            int st = spmv_enqueue(h, h->x_stage, h->y_stage, false, true);
+            if (st != MX_OK) return st;
+        }
+        HCK(cudaEventRecord(ev.e1, h->stream));
+        HCK(cudaEventSynchronize(ev.e1));
+        HCK(cudaEventElapsedTime(&ms[v], ev.e0, ev.e1));
+    }
+    h->slab_ms_plain = ms[0] / 5;
+    h->slab_ms_slabbed = ms[1] / 5;
+    h->use_slabs = ms[1] < ms[0];
+    if (!h->use_slabs) col_slabs_free(h->slabs, h->stream);
     return MX_OK;
 }
 
@@ -514,6 +592,7 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         h->planned = true;  // the tuner runs real products
         const auto t0 = std::chrono::steady_clock::now();
         int tst = tune_prefetch(h);
+        if (tst == MX_OK) tst = tune_col_slabs(h);
         if (tst != MX_OK) {
             drop_plan(h);
             return tst;
@@ -802,6 +881,11 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
 int mx_spmv_launches(mx_handle_t h) {
     if (!h || !h->planned) return 0;
     int n = resid_launches(h->resid);
+    if (h->use_slabs) {
+        n = 0;
+        for (int k = 0; k < h->slabs.count; ++k)
+            if (h->slabs.plans[k].nnz > 0) n += resid_launches(h->slabs.plans[k]);
+    }
     if (h->stats.active)
         n += (h->use_orig_cols ? 0 : 1) + (h->dd_exec == MX_DD_TILE ? tile_launches(h->tile)
                                          : h->dd_exec == MX_DD_SE ? se_launches(h->se)
@@ -842,6 +926,27 @@ int mx_set_column_space(mx_handle_t h, int mode) {
         HCK(cudaStreamSynchronize(h->stream));
         return tune_colspace(h);
     }
+    return MX_OK;
+}
+
+int mx_set_column_slabs(mx_handle_t h, int count) {
+    if (!h || count < -1 || count == 1 || count > 64) return MX_ERR_INVALID;
+    if (count > 0 && h->dtype != MX_FP64) return h->fail(MX_ERR_INVALID, "column slabs are available for FP64 only");
+    h->slab_mode = count;
+    if (h->planned && !h->stats.active) {
+        HCK(cudaSetDevice(h->device));
+        HCK(cudaStreamSynchronize(h->stream));
+        col_slabs_free(h->slabs, h->stream);
+        return tune_col_slabs(h);
+    }
+    return MX_OK;
+}
+
+int mx_column_slabs(mx_handle_t h, int *count, float *ms_plain, float *ms_slabbed) {
+    if (!h) return MX_ERR_INVALID;
+    if (count) *count = h->use_slabs ? h->slabs.count : 0;
+    if (ms_plain) *ms_plain = h->slab_ms_plain;
+    if (ms_slabbed) *ms_slabbed = h->slab_ms_slabbed;
     return MX_OK;
 }
 

@@ -66,6 +66,16 @@ struct ResidPlan {
     void *head = nullptr;      // [num_tiles] accumulate-type partial of a first row that began in an earlier tile
 };
 
+// Column-slab execution of one CSR matrix (col_slabs.cu): the matrix cut into vertical slabs of `width` columns, each
+// stored as a CSR of its own over its non-empty rows and multiplied in a pass of its own that adds into y, so that the
+// x range a pass gathers from stays resident in L2.  Owned.
+struct ColSlabs {
+    int count = 0, width = 0;
+    ResidPlan *plans = nullptr;  // [count] host array; every plan owns its row tables, the struct owns col/val
+    int **col = nullptr;         // [count] host array of device pointers
+    void **val = nullptr;        // [count]
+};
+
 // Plain CSR on the device (non-owning view).
 struct CsrDev {
     int n_rows = 0, n_cols = 0, nnz = 0;
@@ -139,6 +149,7 @@ struct PartArrays {
 
 // ---- launchers (each returns the cudaError_t of its launches) ----
 cudaError_t resid_plan_build(int dtype, ResidPlan &plan, cudaStream_t s);
+cudaError_t resid_plan_finish(int dtype, ResidPlan &plan, cudaStream_t s);
 void resid_plan_free(ResidPlan &plan, cudaStream_t s);
 // y[r] = sum_r (+ y_in[r] when accumulate) (+ ytile[r] for rows flagged in hotmask).  ytile is of the
 // accumulate type (float for FP16, double for FP64); hotmask has one bit per row.
@@ -156,6 +167,11 @@ cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, vo
                              long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
                              bool chained = false, void *mc_y = nullptr);
 int resid_launches(const ResidPlan &plan);
+// Cuts A (rows with ascending column ids) into `count` column slabs; *status = MX_ERR_INVALID when a row is not sorted.
+cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, ColSlabs &out, int *status, cudaStream_t s);
+void col_slabs_free(ColSlabs &S, cudaStream_t s);
+// y = A x (value type): y is cleared, then every slab adds its part.  2 launches per slab.
+cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
 // largest hot-column prefix (columns, rounded down to 16 bytes of values) the persistent CSR kernel can hold in shared
 // memory for this value type; 0 when `d_cols` is too small to be worth a persistent launch
 int resid_hot_cols_budget(int dtype, int d_cols);

@@ -408,3 +408,41 @@ def test_core_dense_block_through_each_executor(name, n, tau):
         np.testing.assert_array_equal(_bits(before[k]), _bits(after[k]), err_msg=k)
     assert h.device_error() == 0
     h.close()
+
+
+def test_column_slab_execution_matches_the_plain_kernel():
+    """tau = (0,0), FP64: the product cut into column slabs (one accumulate pass per slab) equals the reference within
+    tolerance, is reproducible bit for bit, and is refused (plain kernel kept) when rows are not sorted by column."""
+    m = synth.generate("c5", n=300_000)
+    n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    h = mx.MatXtract(FP64)
+    h.upload_csr(n, n, rp, ci, val)
+    h.partition(0.0, 0.0)
+    assert h.column_slabs[0] == 0          # x (2.4 MB) fits L2: the automatic rule leaves the plain kernel
+    y_plain = h.spmv_host(x)
+    launches_plain = h.launches_per_spmv
+    for count in (2, 7, 16):
+        h.set_column_slabs(count)
+        assert h.column_slabs[0] == count and h.launches_per_spmv > launches_plain
+        y1 = h.spmv_host(x)
+        y2 = h.spmv_host(x)
+        np.testing.assert_array_equal(_bits(y1), _bits(y2))
+        check_y(FP64, y1, rp, ci, val, x)
+        assert np.abs(y1 - y_plain).max() <= 1e-13 * max(1.0, np.abs(y_plain).max())
+    h.set_column_slabs(0)
+    assert h.column_slabs[0] == 0
+    np.testing.assert_array_equal(_bits(h.spmv_host(x)), _bits(y_plain))
+    # rows with unsorted columns: the slabs cannot be cut, the plain kernel stays and the result is still right
+    rp_u, ci_u = random_csr(2000, 8, 5, sort_rows=False)
+    val_u, x_u = values(FP64, len(ci_u), 5), values(FP64, 2000, 6)
+    h.upload_csr(2000, 2000, rp_u, ci_u, val_u)
+    h.set_column_slabs(4)
+    h.partition(0.0, 0.0)
+    assert h.column_slabs[0] == 0
+    check_y(FP64, h.spmv_host(x_u), rp_u, ci_u, val_u, x_u)
+    # FP16 handles refuse a forced slab count
+    g = mx.MatXtract(FP16)
+    with pytest.raises(mx.MxError):
+        g.set_column_slabs(4)
+    g.close()
+    h.close()
