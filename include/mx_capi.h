@@ -150,6 +150,38 @@ int mx_spmv_multicast(mx_handle_t h, const void *x_dev, void *const *y_peers, in
  * the caller's barrier across the GPUs. */
 int mx_peer_push(int dtype, void *const *y_peers, int n_peers, int self, long long row_offset, long long n_rows,
                  void *table_dev, void *stream);
+/* ---- multi-GPU: one process drives several GPUs of one box (no counterpart in the reference, which is single-GPU) -- */
+/* Rows are cut into n_devices contiguous slabs of equal non-zero count, bounds[g] = lower_bound(row_ptr, g*nnz/G);
+ * x is replicated, every GPU extracts and multiplies its own slab (rows_g x all columns) through a handle of its own,
+ * and every GPU ends a product with the whole y.  The exchange of y is either MX_MG_EXCHANGE_PEER (default where the
+ * GPUs can address each other's memory): the SpMV kernels store their finished rows into every GPU's buffer over
+ * NVLink (mx_spmv_peers) and the GPUs then wait for each other's CUDA events in stream order - nothing spins; or
+ * MX_MG_EXCHANGE_NCCL: every GPU writes its own rows and NCCL broadcasts the slabs (ncclCommInitAll; libnccl.so.2 is
+ * bound at run time).  One host thread per mx_mg_t.  Devices must be distinct. */
+typedef struct mx_mg_s *mx_mg_t;
+enum { MX_MG_EXCHANGE_PEER = 0, MX_MG_EXCHANGE_NCCL = 1 };
+/* devices = NULL: GPUs 0 .. n_devices-1.  n_devices <= 8. */
+int mx_mg_create(mx_mg_t *mg, int n_devices, const int *devices, int dtype);
+int mx_mg_destroy(mx_mg_t mg);
+const char *mx_mg_last_error_string(mx_mg_t mg);
+int mx_mg_set_exchange(mx_mg_t mg, int mode);
+/* The nnz-balanced row boundaries alone (host code, no GPU): bounds has n_parts + 1 entries. */
+int mx_mg_partition_rows(const int *row_ptr, int n_rows, int n_parts, int *bounds);
+/* Cuts the host CSR matrix with mx_mg_partition_rows and uploads slab g to GPU g (validated like mx_upload_csr). */
+int mx_mg_upload_csr(mx_mg_t mg, int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind,
+                     const void *val);
+/* mx_partition on every slab; per_device (may be NULL) receives n_devices stats. */
+int mx_mg_partition(mx_mg_t mg, double tau_c, double tau_r, mx_partition_stats *per_device);
+int mx_mg_bounds(mx_mg_t mg, int *bounds); /* n_devices + 1 entries */
+int mx_mg_devices(mx_mg_t mg);
+mx_handle_t mx_mg_handle(mx_mg_t mg, int g); /* the handle of slab g, e.g. for mx_set_dd_executor */
+/* y = A x with HOST x (n_cols values) and y (n_rows values): x to every GPU, product + exchange, y from GPU 0. */
+int mx_mg_spmv(mx_mg_t mg, const void *x_host, void *y_host);
+/* The whole y as GPU g holds it after the last product (every GPU holds the same). */
+int mx_mg_download_y(mx_mg_t mg, int g, void *y_host);
+/* warm + iters products on device-resident copies of x; *ms_per_spmv = device time of the slowest GPU / iters. */
+int mx_mg_spmv_timed(mx_mg_t mg, const void *x_host, int warm, int iters, float *ms_per_spmv);
+
 /* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
 /* Timing loop on the device: `warm` untimed and `iters` timed repetitions (the reference uses 200 and

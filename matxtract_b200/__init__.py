@@ -18,6 +18,8 @@ from .capi import (  # noqa: F401
     HOT_ON,
     FP64,
     MatXtract,
+    MultiGpu,
+    mg_partition_rows,
     MxError,
     PartitionStats,
     cdspmv,

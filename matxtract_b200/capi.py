@@ -80,6 +80,19 @@ SYMBOLS = {
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
     "mx_spmv_multicast": (_i, [_vp, _vp, C.POINTER(_vp), _i, _vp, C.c_longlong]),
     "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
+    "mx_mg_create": (_i, [C.POINTER(_vp), _i, _ip, _i]),
+    "mx_mg_destroy": (_i, [_vp]),
+    "mx_mg_last_error_string": (C.c_char_p, [_vp]),
+    "mx_mg_set_exchange": (_i, [_vp, _i]),
+    "mx_mg_partition_rows": (_i, [_vp, _i, _i, _vp]),
+    "mx_mg_upload_csr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
+    "mx_mg_partition": (_i, [_vp, _d, _d, C.POINTER(PartitionStats)]),
+    "mx_mg_bounds": (_i, [_vp, _vp]),
+    "mx_mg_devices": (_i, [_vp]),
+    "mx_mg_handle": (_vp, [_vp, _i]),
+    "mx_mg_spmv": (_i, [_vp, _vp, _vp]),
+    "mx_mg_download_y": (_i, [_vp, _i, _vp]),
+    "mx_mg_spmv_timed": (_i, [_vp, _vp, _i, _i, C.POINTER(C.c_float)]),
     "mx_read_matrix_market": (_i, [C.c_char_p, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
                                    C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
                                    C.POINTER(_vp)]),
@@ -354,6 +367,81 @@ class MatXtract:
         e = C.c_int()
         self._ck(lib().mx_device_error(self._h, C.byref(e)))
         return e.value
+
+
+MG_EXCHANGE_PEER, MG_EXCHANGE_NCCL = 0, 1
+
+
+def mg_partition_rows(row_ptr, n_parts: int) -> np.ndarray:
+    """nnz-balanced row boundaries (host code): bounds[g] = lower_bound(row_ptr, g * nnz / n_parts)."""
+    row_ptr = _c(row_ptr, np.int32)
+    bounds = np.empty(n_parts + 1, np.int32)
+    _raise(lib().mx_mg_partition_rows(_ptr(row_ptr), len(row_ptr) - 1, n_parts, _ptr(bounds)))
+    return bounds
+
+
+class MultiGpu:
+    """One matrix over several GPUs of one box, driven by this process (mx_mg_* of the C ABI)."""
+
+    def __init__(self, dtype: int, n_devices: int, devices=None):
+        self._h = C.c_void_p()
+        self.dtype, self.n = dtype, n_devices
+        devs = None if devices is None else (C.c_int * n_devices)(*devices)
+        st = lib().mx_mg_create(C.byref(self._h), n_devices, devs, dtype)
+        if st != 0:
+            raise MxError(st, lib().mx_status_string(st).decode())
+        self.n_rows = self.n_cols = 0
+
+    def _ck(self, st):
+        if st != 0:
+            raise MxError(st, lib().mx_mg_last_error_string(self._h).decode())
+
+    def upload_csr(self, n_rows, n_cols, row_ptr, col_ind, val):
+        row_ptr, col_ind, val = _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(val, np_dtype(self.dtype))
+        self._ck(lib().mx_mg_upload_csr(self._h, n_rows, n_cols, len(col_ind), _ptr(row_ptr), _ptr(col_ind), _ptr(val)))
+        self.n_rows, self.n_cols = n_rows, n_cols
+
+    def partition(self, tau_c, tau_r):
+        stats = (PartitionStats * self.n)()
+        self._ck(lib().mx_mg_partition(self._h, float(tau_c), float(tau_r), stats))
+        return list(stats)
+
+    def set_exchange(self, mode: int):
+        self._ck(lib().mx_mg_set_exchange(self._h, mode))
+
+    @property
+    def bounds(self) -> np.ndarray:
+        b = np.empty(self.n + 1, np.int32)
+        self._ck(lib().mx_mg_bounds(self._h, _ptr(b)))
+        return b
+
+    def spmv(self, x: np.ndarray) -> np.ndarray:
+        x = _c(x, np_dtype(self.dtype))
+        y = np.empty(self.n_rows, np_dtype(self.dtype))
+        self._ck(lib().mx_mg_spmv(self._h, _ptr(x), _ptr(y)))
+        return y
+
+    def y_of(self, g: int) -> np.ndarray:
+        y = np.empty(self.n_rows, np_dtype(self.dtype))
+        self._ck(lib().mx_mg_download_y(self._h, g, _ptr(y)))
+        return y
+
+    def spmv_timed(self, x: np.ndarray, warm=5, iters=20) -> float:
+        x = _c(x, np_dtype(self.dtype))
+        ms = C.c_float()
+        self._ck(lib().mx_mg_spmv_timed(self._h, _ptr(x), warm, iters, C.byref(ms)))
+        return ms.value
+
+    def close(self):
+        if self._h:
+            lib().mx_mg_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def _raise(st):

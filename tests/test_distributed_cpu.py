@@ -83,3 +83,23 @@ def test_all_gather_assembles_y_on_gloo(world, balance):
     assert all(ok for _, ok, _, _ in res)
     if balance == "nnz":
         assert len({tuple(s) for _, _, s, _ in res}) == 1  # every rank computed the same boundaries
+
+
+def test_c_abi_row_partitioner_matches_the_python_one():
+    """mx_mg_partition_rows (host code of the multi-GPU entry) = lower_bound(row_ptr, g * nnz / G), monotone."""
+    import matxtract_b200 as mx
+    from matxtract_b200.distributed import nnz_balanced_bounds
+
+    rng = np.random.default_rng(3)
+    for n, world in ((1, 1), (7, 3), (1000, 8), (1000, 1), (50, 8)):
+        lens = rng.integers(0, 40, n)
+        lens[rng.random(n) < 0.3] = 0
+        rp = np.zeros(n + 1, np.int32)
+        np.cumsum(lens, out=rp[1:])
+        b = mx.mg_partition_rows(rp, world)
+        assert b.tolist() == nnz_balanced_bounds(rp, world)
+        assert b[0] == 0 and b[-1] == n and (np.diff(b) >= 0).all()
+    # all non-zeros in one row: every boundary but the last collapses onto it
+    rp = np.zeros(11, np.int32)
+    rp[6:] = 100
+    assert mx.mg_partition_rows(rp, 4).tolist() == nnz_balanced_bounds(rp, 4)
