@@ -426,29 +426,22 @@ static int tune_col_slabs(mx_handle_t h) {
     int l2 = 0;
     cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->device);
     const size_t xbytes = val_bytes(h->dtype) * (size_t)h->n_cols;
-    constexpr size_t SLAB_X_BYTES = 32u << 20;  // the x range of one pass
-    int count = h->slab_mode;
-    if (count < 0) {
-        if (l2 <= 0 || xbytes <= (size_t)l2) return MX_OK;  // x fits L2: nothing to gain
-        count = (int)std::min<size_t>(64, (xbytes + SLAB_X_BYTES - 1) / SLAB_X_BYTES);
-    }
-    if (count < 2) return MX_OK;
     CsrDev A;
     A.n_rows = h->n_rows, A.n_cols = h->n_cols, A.nnz = h->nnz;
     A.row_ptr = h->row_ptr, A.col_ind = h->col_ind, A.val = h->val;
-    int status = MX_OK;
-    HCK(col_slabs_build(h->dtype, A, count, h->slabs, &status, h->stream));
-    if (status != MX_OK) return MX_OK;  // rows not sorted by column: the plain kernel stays
-    if (h->slab_mode > 0) {
-        h->use_slabs = true;
+    if (h->slab_mode > 0) {  // forced
+        int status = MX_OK;
+        HCK(col_slabs_build(h->dtype, A, h->slab_mode, h->slabs, &status, h->stream));
+        h->use_slabs = status == MX_OK;  // rows not sorted by column: the plain kernel stays
         return MX_OK;
     }
+    if (l2 <= 0 || xbytes <= (size_t)l2) return MX_OK;  // x fits L2: nothing to gain
+    // candidates: x ranges of 96, 64 and 32 MB per pass (fewer passes re-read y less often, narrower ones sit in L2
+    // more safely); each is built, timed against the plain kernel on scratch vectors, and the fastest stays
     EventPair ev;
     HCK(ev.create());
     HCK(cudaMemsetAsync(h->x_stage, 0, xbytes, h->stream));
-    float ms[2] = {0, 0};
-    for (int v = 0; v < 2; ++v) {
-        h->use_slabs = v == 1;
+    auto time_product = [&](float *ms) -> int {
         for (int i = 0; i < 2 + 5; ++i) {
             if (i == 2) HCK(cudaEventRecord(ev.e0, h->stream));
             int st = spmv_enqueue(h, h->x_stage, h->y_stage, false, true);
@@ -456,12 +449,44 @@ static int tune_col_slabs(mx_handle_t h) {
         }
         HCK(cudaEventRecord(ev.e1, h->stream));
         HCK(cudaEventSynchronize(ev.e1));
-        HCK(cudaEventElapsedTime(&ms[v], ev.e0, ev.e1));
+        HCK(cudaEventElapsedTime(ms, ev.e0, ev.e1));
+        *ms /= 5;
+        return MX_OK;
+    };
+    int st = time_product(&h->slab_ms_plain);
+    if (st != MX_OK) return st;
+    float best = h->slab_ms_plain;
+    int best_count = 0, last = 0;
+    for (size_t mb : {96, 64, 32}) {
+        const int count = (int)std::min<size_t>(64, (xbytes + (mb << 20) - 1) / (mb << 20));
+        if (count < 2 || count == last) continue;
+        last = count;
+        ColSlabs trial;
+        int status = MX_OK;
+        HCK(col_slabs_build(h->dtype, A, count, trial, &status, h->stream));
+        if (status != MX_OK) return MX_OK;  // rows not sorted by column
+        ColSlabs keep = h->slabs;
+        h->slabs = trial;
+        h->use_slabs = true;
+        float ms = 0;
+        st = time_product(&ms);
+        h->use_slabs = false;
+        h->slabs = keep;
+        if (st != MX_OK) {
+            col_slabs_free(trial, h->stream);
+            return st;
+        }
+        if (h->slab_ms_slabbed == 0 || ms < h->slab_ms_slabbed) h->slab_ms_slabbed = ms;
+        if (ms < best) {
+            best = ms;
+            best_count = count;
+            col_slabs_free(h->slabs, h->stream);
+            h->slabs = trial;
+        } else {
+            col_slabs_free(trial, h->stream);
+        }
     }
-    h->slab_ms_plain = ms[0] / 5;
-    h->slab_ms_slabbed = ms[1] / 5;
-    h->use_slabs = ms[1] < ms[0];
-    if (!h->use_slabs) col_slabs_free(h->slabs, h->stream);
+    h->use_slabs = best_count > 0;
     return MX_OK;
 }
 
