@@ -300,8 +300,9 @@ int mx_se_tcspmv(int dtype, const void *csrVal, const int *csrRowPtr, const int 
  * process exits), which bounds the problem: at most MX_STATIC_MAX_ROWS rows and MX_STATIC_MAX_NNZ non-zeros, else
  * MX_ERR_TOO_LARGE.  All calls share that array: do not let two calls overlap on the GPU (they would race on it).
  * The call synchronises `stream` once (it reads one count back).  The first call on a device looks up the array's
- * device address; make that first call before starting any stream capture.  `stream` is a cudaStream_t (NULL = the
- * default stream). */
+ * device address; make that first call before starting any stream capture.  The looked-up address is kept for the
+ * life of the process and is not valid after a cudaDeviceReset of that device.  `stream` is a cudaStream_t (NULL =
+ * the default stream). */
 #define MX_STATIC_MAX_ROWS (1 << 20)
 #define MX_STATIC_MAX_NNZ (1 << 26)
 #define MX_STATIC_SCRATCH_BYTES (24u << 20)

@@ -921,13 +921,17 @@ cudaError_t gather_vector(int dtype, const void *x, const int *perm, void *out, 
 // streams, or different host threads) race on it — issue them one after the other.
 // In host code `g_static_scratch` is only a stand-in for the device symbol, not a device address: its address is
 // looked up once per device with cudaGetSymbolAddress (with that device current) and that pointer is what the kernels
-// get.  The first call on a device performs this look-up, so it should happen before any stream capture begins.
+// get.  The first call on a device performs this look-up, so it should happen before any stream capture begins.  The
+// address is cached for the life of the process: it does not survive a cudaDeviceReset of that device.  Every call
+// also reads one count back and synchronises the stream once.
 // ---------------------------------------------------------------------------------------------------------------
 namespace mx {
 namespace {
 
 constexpr size_t ST_ROWS = MX_STATIC_MAX_ROWS;
-constexpr size_t ST_TILES = (size_t)MX_STATIC_MAX_NNZ / (RESID_THREADS * ResidCfg<double>::IPT) + 1;  // FP64 tiles are the smaller
+// tile slots are sized for the value type with the smaller tile (more tiles per non-zero)
+constexpr int ST_MIN_IPT = ResidCfg<double>::IPT < ResidCfg<__half>::IPT ? ResidCfg<double>::IPT : ResidCfg<__half>::IPT;
+constexpr size_t ST_TILES = (size_t)MX_STATIC_MAX_NNZ / (RESID_THREADS * ST_MIN_IPT) + 1;
 constexpr size_t ST_CUB_TEMP = 1u << 20;
 // layout (byte offsets, each region 256-byte aligned)
 constexpr size_t st_align(size_t b) { return (b + 255) & ~(size_t)255; }

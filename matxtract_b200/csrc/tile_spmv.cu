@@ -117,7 +117,8 @@ struct CtaDesc {  // computed at plan time
     int seg0, seg1;  // work segments [seg0, seg1)
     int f0, f1;      // fragments [f0, f1) they cover
     int v0, v1;      // packed values [v0, v1)
-    int pad0, pad1;
+    int full;        // 1: every fragment of the run is completely filled (no bitmap decode needed)
+    int pad1;
 };
 
 constexpr int STAGE_WARPS = 4;   // warps per CTA (8 measured slower)
@@ -238,6 +239,90 @@ __device__ __forceinline__ void run_segment(const int4 sd, int s, int lane, cons
     }
 }
 
+// A work segment whose fragments are all completely filled needs neither its bitmaps nor its value offsets: fragment f
+// holds the values [v(f0) + (f - f0) * 8K, ...) in bit order, so every lane streams its own values straight from global
+// memory (coalesced, 256 / 128 bytes per fragment) and only the K x-indices of a fragment are shared by its 8 rows.
+// Per non-zero that is sizeof(value) + 4/8 bytes (FP64: 8.5 B against 12 B as CSR).
+__device__ __forceinline__ double ldg_nc_stream(const double *p) {
+    double r;
+    asm volatile("ld.global.nc.L1::no_allocate.f64 %0, [%1];" : "=d"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ unsigned ldg_nc_stream(const unsigned *p) {
+    unsigned r;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+
+template <typename B, typename V, int K, typename OutT, bool ACCUM>
+__device__ __forceinline__ void run_segment_full(const int4 sd, int s, int lane, int vseg, const V *__restrict__ tcVal,
+                                                 const int *__restrict__ AToX, const V *__restrict__ x_d,
+                                                 const int *__restrict__ panelFirstSeg,
+                                                 typename std::conditional<sizeof(V) == 8, double, float>::type *partial,
+                                                 unsigned *panelCount, OutT *out, const int *row_map, int dRows) {
+    const int p = sd.x, f0 = sd.y, f1 = sd.z;  // vseg: value offset of fragment f0
+    const int myRow = p * 8 + (lane >> 2);
+    const int outRow = (row_map && myRow < dRows) ? __ldg(row_map + myRow) : myRow;
+    if constexpr (sizeof(V) == 8) {
+        const int kx = lane & 3;
+        const double *vp = tcVal + vseg + lane;
+        const int *xp = AToX + (size_t)f0 * 4 + kx;
+        double c0 = 0.0, c1 = 0.0, e0 = 0.0, e1 = 0.0;
+        int f = f0;
+#pragma unroll 4
+        for (; f + 1 < f1; f += 2, vp += 64, xp += 8) {
+            const double aA = ldg_nc_stream(vp), aB = ldg_nc_stream(vp + 32);
+            const double bA = __ldg(x_d + __ldg(xp)), bB = __ldg(x_d + __ldg(xp + 4));
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                         : "+d"(c0), "+d"(c1)
+                         : "d"(aA), "d"(bA));
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                         : "+d"(e0), "+d"(e1)
+                         : "d"(aB), "d"(bB));
+        }
+        if (f < f1) {
+            const double aA = ldg_nc_stream(vp);
+            const double bA = __ldg(x_d + __ldg(xp));
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                         : "+d"(c0), "+d"(c1)
+                         : "d"(aA), "d"(bA));
+        }
+        finish_staged<double, OutT, ACCUM>(c0 + e0, (lane & 3) == 0, lane >> 2, lane, p, s, sd.w, myRow, outRow, dRows,
+                                           panelFirstSeg, (double *)partial, panelCount, out);
+    } else {
+        // lane l owns bits 2l, 2l+1 of every fragment: one 4-byte load per fragment
+        const int g = lane >> 2, tq = lane & 3;
+        const unsigned *vp = reinterpret_cast<const unsigned *>(tcVal + vseg) + lane;
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+        for (int f = f0; f < f1; f += 4, vp += 128) {
+            unsigned a[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[j] = f + j < f1 ? ldg_nc_stream(vp + 32 * j) : 0u;
+            unsigned b0 = 0u, b1 = 0u;
+            if (g < 2) {
+                const int fb = f + 2 * g;
+                if (fb < f1) {
+                    const int2 ix = __ldg(reinterpret_cast<const int2 *>(AToX + (size_t)fb * 8 + 2 * tq));
+                    b0 = (unsigned)__half_as_ushort(__ldg(x_d + ix.x)) |
+                         ((unsigned)__half_as_ushort(__ldg(x_d + ix.y)) << 16);
+                }
+                if (fb + 1 < f1) {
+                    const int2 ix = __ldg(reinterpret_cast<const int2 *>(AToX + (size_t)(fb + 1) * 8 + 2 * tq));
+                    b1 = (unsigned)__half_as_ushort(__ldg(x_d + ix.x)) |
+                         ((unsigned)__half_as_ushort(__ldg(x_d + ix.y)) << 16);
+                }
+            }
+            asm volatile(
+                "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                "{%0,%1,%2,%3};"
+                : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+                : "r"(a[0]), "r"(a[2]), "r"(a[1]), "r"(a[3]), "r"(b0), "r"(b1));
+        }
+        finish_staged<float, OutT, ACCUM>(c0 + c3, tq == 0, g, lane, p, s, sd.w, myRow, outRow, dRows, panelFirstSeg,
+                                          (float *)partial, panelCount, out);
+    }
+}
+
 template <typename B, typename V, int K, typename OutT, bool ACCUM, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
     tile_kernel_staged(const V *__restrict__ x_d, const int *__restrict__ fragPtr, const B *__restrict__ fragBit,
@@ -249,8 +334,16 @@ __global__ void __launch_bounds__(NWARPS * 32)
     extern __shared__ __align__(16) unsigned char stage[];
     uint64_t *bar = reinterpret_cast<uint64_t *>(stage);
     const CtaDesc d = desc[blockIdx.x];
-    const StageLayout<B, V, K> L(d.f0, d.f1, d.v0, d.v1);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (d.full) {  // nothing to decode: no staging, values stream straight into the MMA operands
+        for (int s = d.seg0 + warp; s < d.seg1; s += NWARPS) {
+            const int4 sd = __ldg(segDesc + s);
+            run_segment_full<B, V, K, OutT, ACCUM>(sd, s, lane, d.v0 + (sd.y - d.f0) * 8 * K, tcVal, AToX, x_d,
+                                                   panelFirstSeg, partial, panelCount, out, row_map, dRows);
+        }
+        return;
+    }
+    const StageLayout<B, V, K> L(d.f0, d.f1, d.v0, d.v1);
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -345,7 +438,7 @@ __global__ void cta_desc_kernel(const long long *__restrict__ prefix, const int 
     CtaDesc d;
     d.seg0 = c == 0 ? 0 : first(c);
     d.seg1 = first(c + 1);
-    d.pad0 = d.pad1 = 0;
+    d.full = d.pad1 = 0;
     if (d.seg1 > d.seg0) {
         d.f0 = segBegin[d.seg0];
         d.f1 = segEnd[d.seg1 - 1];
@@ -354,6 +447,7 @@ __global__ void cta_desc_kernel(const long long *__restrict__ prefix, const int 
     }
     d.v0 = fragPtr[d.f0];
     d.v1 = fragPtr[d.f1];
+    d.full = d.f1 > d.f0 && (long long)(d.v1 - d.v0) == (long long)(d.f1 - d.f0) * 8 * K;
     desc[c] = d;
     atomicMax(maxBytes, StageLayout<B, V, K>(d.f0, d.f1, d.v0, d.v1).total());
 }

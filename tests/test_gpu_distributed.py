@@ -37,7 +37,10 @@ for name, n, tau in (("c2", 60000, (0.46, 0.33)), ("c3", 8 * 4000, (0.5, 0.5)), 
     assert sum(d.bounds[g + 1] - d.bounds[g] for g in range(world)) == n
     # the same product with the all-gather fused into the kernels (peer stores + one barrier): identical bits
     for how in ("epilogue", "push", "multicast"):
-        f = D.DistributedSpMV(dtype, n, m["row_ptr"], m["col_ind"], m["val"], rank, world, tau=tau, fused=how)
+        # same executor of the core-dense block as the first handle (the automatic choice is a timing and may differ
+        # between two handles; the executors sum in different orders)
+        f = D.DistributedSpMV(dtype, n, m["row_ptr"], m["col_ind"], m["val"], rank, world, tau=tau, fused=how,
+                              dd_executor=d.handle.dd_executor if d.stats.active else None)
         if how == "multicast" and not f.peer_y.multicast_ptr:
             print(f"rank {rank} {name}: no multicast address on this box, multicast stores not exercised", flush=True)
             f.close()

@@ -76,3 +76,21 @@ def test_static_entry_point_rejects_what_does_not_fit():
     with pytest.raises(mx.MxError) as e:
         capi.csr_spmv_static(mx.FP64, 8, 8, -1, t, t, v, v, v)
     assert e.value.status == 1
+
+
+def test_static_entry_point_takes_no_device_memory():
+    """After a first call (which looks up the scratch array's address), repeated calls leave the amount of free device
+    memory unchanged: nothing is allocated, from the driver or from a pool, at call time."""
+    m = synth.generate("c5", n=40_000)
+    n, rp, ci, val = m["n"], m["row_ptr"], m["col_ind"], m["val"]
+    d_rp, d_ci, d_val = _dev(rp.astype(np.int32)), _dev(ci.astype(np.int32)), _dev(val)
+    x_dev = _dev(m["x"])
+    y = torch.zeros(n, dtype=torch.float64, device="cuda")
+    capi.csr_spmv_static(mx.FP64, n, n, len(ci), d_rp, d_ci, d_val, x_dev, y, stream=0)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        capi.csr_spmv_static(mx.FP64, n, n, len(ci), d_rp, d_ci, d_val, x_dev, y, stream=0)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
