@@ -76,6 +76,24 @@ typedef struct {
  * row-partitioned matrix) is accepted as well and is extracted on its own. */
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats);
 int mx_partition_stats_get(mx_handle_t h, mx_partition_stats *stats);
+/* Extraction of one row slab of a matrix that is spread over several GPUs, with the reference's rankings taken over
+ * the WHOLE matrix (the reference ranks all columns and all rows of its one matrix, test/test_autotc_spmv.cpp:1122-1141,
+ * 1240-1267): the slabs' hot columns are then the whole matrix's hot columns (same dCols, same xperm on every GPU) and
+ * the slabs' hot rows together are the whole matrix's hot rows.  The caller supplies what needs an exchange:
+ *   1. mx_col_counts on every slab, summed over the slabs                      -> global_col_counts_dev, global_nnz
+ *   2. mx_row_counts_in_hot_columns on every slab, concatenated in row order   -> the whole matrix's row counts
+ *   3. mx_rank_cut(counts, n_rows, (int)((float)global_nnz * (float)tau_r))     -> out[2], out[3] = the row cut
+ *   4. mx_partition_global on every slab with that cut and the slab's first global row index.
+ * mx_mg_partition does these steps itself.  All *_dev pointers are device memory on the handle's GPU. */
+int mx_col_counts(mx_handle_t h, int *counts_dev /* [n_cols] */);
+int mx_row_counts_in_hot_columns(mx_handle_t h, double tau_c, const int *global_col_counts_dev, long long global_nnz,
+                                 int *row_counts_dev /* [n_rows] */);
+/* counts ranked descending (ties: lower index first); out = {k, sum, count of the k-th, index of the k-th} for the
+ * smallest prefix k >= 1 whose sum reaches threshold; k = 0 when none does. */
+int mx_rank_cut(mx_handle_t h, const int *counts_dev, int n, long long threshold, long long out[4]);
+int mx_partition_global(mx_handle_t h, double tau_c, double tau_r, const int *global_col_counts_dev,
+                        long long global_nnz, int row_cut_count, long long row_cut_index, long long row_offset,
+                        mx_partition_stats *stats);
 /* The int32 limit of the fragment format (the reference's indT, include/common.h:79, indexes both the fragments and
  * the fragK x-index slots of each, test/test_autotc_spmv.cpp:1384-1404): MX_OK when `total_frags` fragments can be
  * indexed, MX_ERR_OVERFLOW when not.  mx_partition applies this rule to the fragment total (taken in 64 bits on the
@@ -170,8 +188,12 @@ int mx_mg_partition_rows(const int *row_ptr, int n_rows, int n_parts, int *bound
 /* Cuts the host CSR matrix with mx_mg_partition_rows and uploads slab g to GPU g (validated like mx_upload_csr). */
 int mx_mg_upload_csr(mx_mg_t mg, int n_rows, int n_cols, int nnz, const int *row_ptr, const int *col_ind,
                      const void *val);
-/* mx_partition on every slab; per_device (may be NULL) receives n_devices stats. */
+/* Extraction on every slab; per_device (may be NULL) receives n_devices stats.  With more than one GPU and tau != (0,0)
+ * the rankings are those of the whole matrix (column counts summed over the GPUs, row counts gathered, one cut):
+ * see mx_partition_global. */
 int mx_mg_partition(mx_mg_t mg, double tau_c, double tau_r, mx_partition_stats *per_device);
+/* on != 0: every slab ranks its own columns and rows (mx_partition per slab) instead of the whole matrix's */
+int mx_mg_set_local_ranking(mx_mg_t mg, int on);
 int mx_mg_bounds(mx_mg_t mg, int *bounds); /* n_devices + 1 entries */
 int mx_mg_devices(mx_mg_t mg);
 mx_handle_t mx_mg_handle(mx_mg_t mg, int g); /* the handle of slab g, e.g. for mx_set_dd_executor */

@@ -67,6 +67,11 @@ SYMBOLS = {
     "mx_sync": (_i, [_vp]),
     "mx_upload_csr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "mx_partition": (_i, [_vp, _d, _d, C.POINTER(PartitionStats)]),
+    "mx_col_counts": (_i, [_vp, _vp]),
+    "mx_row_counts_in_hot_columns": (_i, [_vp, _d, _vp, C.c_longlong, _vp]),
+    "mx_rank_cut": (_i, [_vp, _vp, _i, C.c_longlong, C.POINTER(C.c_longlong * 4)]),
+    "mx_partition_global": (_i, [_vp, _d, _d, _vp, C.c_longlong, _i, C.c_longlong, C.c_longlong,
+                                 C.POINTER(PartitionStats)]),
     "mx_partition_stats_get": (_i, [_vp, C.POINTER(PartitionStats)]),
     "mx_save_partition": (_i, [_vp, C.c_char_p]),
     "mx_load_partition": (_i, [_vp, C.c_char_p, C.POINTER(PartitionStats)]),
@@ -87,6 +92,7 @@ SYMBOLS = {
     "mx_mg_partition_rows": (_i, [_vp, _i, _i, _vp]),
     "mx_mg_upload_csr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "mx_mg_partition": (_i, [_vp, _d, _d, C.POINTER(PartitionStats)]),
+    "mx_mg_set_local_ranking": (_i, [_vp, _i]),
     "mx_mg_bounds": (_i, [_vp, _vp]),
     "mx_mg_devices": (_i, [_vp]),
     "mx_mg_handle": (_vp, [_vp, _i]),
@@ -195,6 +201,30 @@ class MatXtract:
     def partition(self, tau_c: float = 0.0, tau_r: float = 0.0) -> PartitionStats:
         st = PartitionStats()
         self._ck(lib().mx_partition(self._h, float(tau_c), float(tau_r), C.byref(st)))
+        self.stats = st
+        return st
+
+    # ---- the whole matrix's rankings for a slab of a matrix spread over several GPUs (mx_partition_global) ----
+    def col_counts(self, counts_dev):
+        """Column histogram of this slab into a device int32 buffer of n_cols entries."""
+        self._ck(lib().mx_col_counts(self._h, _ptr(counts_dev)))
+
+    def row_counts_in_hot_columns(self, tau_c, global_col_counts_dev, global_nnz, row_counts_dev):
+        self._ck(lib().mx_row_counts_in_hot_columns(self._h, float(tau_c), _ptr(global_col_counts_dev), int(global_nnz),
+                                                    _ptr(row_counts_dev)))
+
+    def rank_cut(self, counts_dev, n, threshold):
+        """(k, sum, count of the k-th, index of the k-th) of the descending ranking of a device int32 array."""
+        out = (C.c_longlong * 4)()
+        self._ck(lib().mx_rank_cut(self._h, _ptr(counts_dev), int(n), int(threshold), C.byref(out)))
+        return tuple(int(v) for v in out)
+
+    def partition_global(self, tau_c, tau_r, global_col_counts_dev, global_nnz, row_cut_count, row_cut_index,
+                         row_offset) -> PartitionStats:
+        st = PartitionStats()
+        self._ck(lib().mx_partition_global(self._h, float(tau_c), float(tau_r), _ptr(global_col_counts_dev),
+                                           int(global_nnz), int(row_cut_count), int(row_cut_index), int(row_offset),
+                                           C.byref(st)))
         self.stats = st
         return st
 
@@ -408,6 +438,23 @@ class MultiGpu:
 
     def set_exchange(self, mode: int):
         self._ck(lib().mx_mg_set_exchange(self._h, mode))
+
+    def set_local_ranking(self, on: bool):
+        self._ck(lib().mx_mg_set_local_ranking(self._h, int(on)))
+
+    def handle(self, g: int) -> "MatXtract":
+        """A view of slab g's handle (owned by the MultiGpu object: do not close it)."""
+        v = MatXtract.__new__(MatXtract)
+        v._h = C.c_void_p(lib().mx_mg_handle(self._h, g))
+        v.dtype, v.device = self.dtype, g
+        r, c, z = C.c_int(), C.c_int(), C.c_int()
+        lib().mx_dims(v._h, C.byref(r), C.byref(c), C.byref(z))
+        v.n_rows, v.n_cols, v.nnz = r.value, c.value, z.value
+        v.stats = PartitionStats()
+        lib().mx_partition_stats_get(v._h, C.byref(v.stats))
+        v._peer_arrays = {}
+        v.close = lambda: None
+        return v
 
     @property
     def bounds(self) -> np.ndarray:

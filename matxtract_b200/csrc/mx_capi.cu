@@ -516,9 +516,7 @@ static int tune_dd_executor(mx_handle_t h) {
     EventPair ev;
     HCK(ev.create());
     HCK(cudaMemsetAsync(h->x_stage, 0, val_bytes(h->dtype) * (size_t)h->n_cols, h->stream));
-    int best = MX_DD_CSR;
-    for (int ex : {MX_DD_TILE, MX_DD_CSR, MX_DD_SE}) {
-        h->dd_exec = ex;
+    auto time_block = [&](float *ms) -> int {
         for (int i = 0; i < 2 + 6; ++i) {
             if (i == 2) HCK(cudaEventRecord(ev.e0, h->stream));
             int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, false, /*permute=*/i == 0);
@@ -526,9 +524,25 @@ static int tune_dd_executor(mx_handle_t h) {
         }
         HCK(cudaEventRecord(ev.e1, h->stream));
         HCK(cudaEventSynchronize(ev.e1));
-        float ms = 0;
-        HCK(cudaEventElapsedTime(&ms, ev.e0, ev.e1));
-        h->dd_ms[ex] = ms / 6;
+        HCK(cudaEventElapsedTime(ms, ev.e0, ev.e1));
+        *ms /= 6;
+        return MX_OK;
+    };
+    int best = MX_DD_CSR;
+    for (int ex : {MX_DD_TILE, MX_DD_CSR, MX_DD_SE}) {
+        h->dd_exec = ex;
+        int st = time_block(&h->dd_ms[ex]);
+        if (st != MX_OK) return st;
+        if (ex == MX_DD_TILE && h->tile.allFull) {
+            // completely filled fragments: the streaming tile kernel was timed; now the staged one, keep the faster
+            float staged = 0;
+            h->tile.useFull = false;
+            if ((st = time_block(&staged)) != MX_OK) return st;
+            if (staged < h->dd_ms[ex])
+                h->dd_ms[ex] = staged;
+            else
+                h->tile.useFull = true;
+        }
         if (ex == MX_DD_TILE || h->dd_ms[ex] < h->dd_ms[best]) best = ex;
     }
     h->dd_exec = best;
@@ -587,7 +601,65 @@ static int finish_partition(mx_handle_t h) {
     return MX_OK;
 }
 
+static int partition_impl(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats, const GlobalRanking *G);
+
 int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats) {
+    return partition_impl(h, tau_c, tau_r, stats, nullptr);
+}
+
+int mx_partition_global(mx_handle_t h, double tau_c, double tau_r, const int *global_col_counts_dev,
+                        long long global_nnz, int row_cut_count, long long row_cut_index, long long row_offset,
+                        mx_partition_stats *stats) {
+    if (!h || !global_col_counts_dev || global_nnz < 0 || global_nnz > 2147483647LL || row_offset < 0)
+        return MX_ERR_INVALID;
+    GlobalRanking G;
+    G.col_counts = global_col_counts_dev;
+    G.nnz = global_nnz;
+    G.has_row_cut = true;
+    G.row_cut_count = row_cut_count;
+    G.row_cut_index = row_cut_index;
+    G.row_offset = row_offset;
+    return partition_impl(h, tau_c, tau_r, stats, &G);
+}
+
+int mx_col_counts(mx_handle_t h, int *counts_dev) {
+    if (!h || !counts_dev) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_col_counts: no matrix uploaded");
+    HCK(cudaSetDevice(h->device));
+    CsrDev A;
+    A.n_rows = h->n_rows, A.n_cols = h->n_cols, A.nnz = h->nnz;
+    A.row_ptr = h->row_ptr, A.col_ind = h->col_ind, A.val = h->val;
+    HCK(column_counts(A, counts_dev, h->stream));
+    HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+int mx_row_counts_in_hot_columns(mx_handle_t h, double tau_c, const int *global_col_counts_dev, long long global_nnz,
+                                 int *row_counts_dev) {
+    if (!h || !row_counts_dev || global_nnz < 0 || global_nnz > 2147483647LL) return MX_ERR_INVALID;
+    if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_row_counts_in_hot_columns: no matrix uploaded");
+    HCK(cudaSetDevice(h->device));
+    CsrDev A;
+    A.n_rows = h->n_rows, A.n_cols = h->n_cols, A.nnz = h->nnz;
+    A.row_ptr = h->row_ptr, A.col_ind = h->col_ind, A.val = h->val;
+    GlobalRanking G;
+    G.col_counts = global_col_counts_dev;
+    G.nnz = global_nnz;
+    int status = MX_OK;
+    HCK(partition_row_counts(h->dtype, A, (float)tau_c, global_col_counts_dev ? &G : nullptr, row_counts_dev, &status,
+                             h->stream));
+    if (status != MX_OK) return h->fail(status, "tau_c threshold never reached by the ranking prefix");
+    return MX_OK;
+}
+
+int mx_rank_cut(mx_handle_t h, const int *counts_dev, int n, long long threshold, long long out[4]) {
+    if (!h || !counts_dev || !out || n < 0 || threshold < 0 || threshold > 2147483647LL) return MX_ERR_INVALID;
+    HCK(cudaSetDevice(h->device));
+    HCK(rank_cut(counts_dev, n, (int)threshold, out, h->stream));
+    return MX_OK;
+}
+
+static int partition_impl(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *stats, const GlobalRanking *G) {
     if (!h) return MX_ERR_INVALID;
     if (!h->has_matrix) return h->fail(MX_ERR_STATE, "mx_partition: no matrix uploaded");
     if (tau_c < tau_r) return h->fail(MX_ERR_TAU, "col_frac must be greater than hot_frac");
@@ -635,7 +707,7 @@ int mx_partition(mx_handle_t h, double tau_c, double tau_r, mx_partition_stats *
         A.col_ind = h->col_ind;
         A.val = h->val;
         int status = MX_OK;
-        cudaError_t ce = partition_run(h->dtype, A, colProp, rowProp, h->part, h->stats, &status, h->stream);
+        cudaError_t ce = partition_run(h->dtype, A, colProp, rowProp, h->part, h->stats, &status, h->stream, G);
         if (ce != cudaSuccess) {
             drop_plan(h);
             return h->cuda_fail(ce, "partition_run");

@@ -99,6 +99,8 @@ struct TileArrays {
 struct TilePlan {
     TileArrays A;  // view, not owned
     int numSegs = 0, numMultiSegs = 0;
+    bool allFull = false;           // every fragment completely filled: the streaming kernel (no bitmap decode) applies
+    bool useFull = false;           // ... and is in use (the plan-time tuner times it against the staged kernel)
     int *segPanel = nullptr;        // [numSegs]
     int *segBegin = nullptr;        // [numSegs] fragment range of segment s = [segBegin[s], segEnd[s])
     int *segEnd = nullptr;          // [numSegs]
@@ -193,8 +195,22 @@ cudaError_t se_spmv(int dtype, const SePlan &P, const void *x, void *out, bool o
                     cudaStream_t s);
 int se_launches(const SePlan &P);
 
+// Rankings of a matrix whose rows are spread over several GPUs (see partition.cu).
+struct GlobalRanking {
+    const int *col_counts = nullptr;  // [n_cols] column counts of the whole matrix (device)
+    long long nnz = 0;                // its non-zero count
+    bool has_row_cut = false;         // hot rows = those above the whole matrix's row cut:
+    int row_cut_count = 0;            //   count of the last hot row of the whole matrix's ranking
+    long long row_cut_index = 0;      //   and its (global) row index
+    long long row_offset = 0;         // global index of this slab's first row
+};
 cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st,
-                          int *status, cudaStream_t s);
+                          int *status, cudaStream_t s, const GlobalRanking *G = nullptr);
+// per-row count of entries inside the hot columns (the tau_c cut of G's or the slab's own column counts)
+cudaError_t partition_row_counts(int dtype, const CsrDev &A, float tau_c, const GlobalRanking *G, int *row_counts,
+                                 int *status, cudaStream_t s);
+cudaError_t column_counts(const CsrDev &A, int *counts, cudaStream_t s);
+cudaError_t rank_cut(const int *counts, int n, int threshold, long long out[4], cudaStream_t s);
 cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,
                           const void *val_dd, TileArrays &T, int *status, cudaStream_t s);
 // sets DEVERR_INPUT in *dev_err when row_ptr decreases anywhere or a column index is outside [0, n_cols)

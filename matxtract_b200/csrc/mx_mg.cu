@@ -59,12 +59,18 @@ struct mx_mg_s {
     ncclComm_t comm[MG_MAX] = {};
     bool has_comm = false;
     bool ready = false;
+    int local_ranking = 0;  // 1: every slab ranks its own columns and rows instead of the whole matrix's
     std::string err;
     int fail(int st, const std::string &m) {
         err = m;
         return st;
     }
 };
+
+__global__ void k_mg_add(int *__restrict__ a, const int *__restrict__ b, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] += b[i];
+}
 
 #define MGCK(call)                                                                      \
     do {                                                                                \
@@ -278,14 +284,90 @@ int mx_mg_upload_csr(mx_mg_t mg, int n_rows, int n_cols, int nnz, const int *row
     return MX_OK;
 }
 
+// Extraction with the rankings of the whole matrix: column counts summed over the GPUs, per-row counts inside the hot
+// columns gathered in row order, one cut for all.
+static int mg_partition_global(mx_mg_t mg, double tau_c, double tau_r, mx_partition_stats *per_device) {
+    const int n = mg->n;
+    const size_t cbytes = sizeof(int) * (size_t)std::max(mg->n_cols, 1), rbytes = sizeof(int) * (size_t)std::max(mg->n_rows, 1);
+    int *cnt[MG_MAX] = {}, *rowcnt[MG_MAX] = {}, *tmp0 = nullptr, *rows0 = nullptr;
+    struct Cleanup {
+        mx_mg_t mg;
+        int **a, **b, **c, **d;
+        ~Cleanup() {
+            for (int g = 0; g < mg->n; ++g) {
+                cudaSetDevice(mg->dev[g]);
+                if (a[g]) cudaFree(a[g]);
+                if (b[g]) cudaFree(b[g]);
+            }
+            cudaSetDevice(mg->dev[0]);
+            if (*c) cudaFree(*c);
+            if (*d) cudaFree(*d);
+        }
+    } cleanup{mg, cnt, rowcnt, &tmp0, &rows0};
+    for (int g = 0; g < n; ++g) {  // 1. local column histograms
+        MGCK(cudaSetDevice(mg->dev[g]));
+        MGCK(cudaMalloc(&cnt[g], cbytes));
+        MGCK(cudaMalloc(&rowcnt[g], sizeof(int) * (size_t)std::max(mg->bounds[g + 1] - mg->bounds[g], 1)));
+        int st = mx_col_counts(mg->h[g], cnt[g]);
+        if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+    }
+    MGCK(cudaSetDevice(mg->dev[0]));  //    summed on GPU 0, the sum copied back to every GPU
+    MGCK(cudaMalloc(&tmp0, cbytes));
+    MGCK(cudaMalloc(&rows0, rbytes));
+    for (int g = 1; g < n; ++g) {
+        MGCK(cudaMemcpyPeer(tmp0, mg->dev[0], cnt[g], mg->dev[g], cbytes));
+        k_mg_add<<<(mg->n_cols + 255) / 256, 256>>>(cnt[0], tmp0, mg->n_cols);
+        MGCK(cudaGetLastError());
+    }
+    MGCK(cudaDeviceSynchronize());
+    for (int g = 1; g < n; ++g) MGCK(cudaMemcpyPeer(cnt[g], mg->dev[g], cnt[0], mg->dev[0], cbytes));
+    for (int g = 0; g < n; ++g) {  // the copies have landed before any handle's own stream reads them
+        MGCK(cudaSetDevice(mg->dev[g]));
+        MGCK(cudaDeviceSynchronize());
+    }
+    for (int g = 0; g < n; ++g) {  // 2. per-row counts inside the hot columns, gathered in row order on GPU 0
+        int st = mx_row_counts_in_hot_columns(mg->h[g], tau_c, cnt[g], mg->nnz, rowcnt[g]);
+        if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+        const size_t rows = (size_t)(mg->bounds[g + 1] - mg->bounds[g]);
+        if (rows > 0) MGCK(cudaMemcpyPeer(rows0 + mg->bounds[g], mg->dev[0], rowcnt[g], mg->dev[g], sizeof(int) * rows));
+    }
+    MGCK(cudaSetDevice(mg->dev[0]));
+    MGCK(cudaDeviceSynchronize());
+    // 3. the row cut of the whole matrix (threshold computed like the reference: int * float, truncated)
+    const int threshold = (int)mg->nnz * (float)tau_r;
+    long long cut[4] = {0, 0, 0, 0};
+    int st = mx_rank_cut(mg->h[0], rows0, mg->n_rows, threshold, cut);
+    if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[0]));
+    if (cut[0] == 0) return mg->fail(MX_ERR_TAU, "tau_r threshold never reached by the ranking prefix");
+    for (int g = 0; g < n; ++g) {  // 4. every slab extracts with the whole matrix's rankings
+        st = mx_partition_global(mg->h[g], tau_c, tau_r, cnt[g], mg->nnz, (int)cut[2], cut[3], mg->bounds[g],
+                                 per_device ? per_device + g : nullptr);
+        if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+    }
+    return MX_OK;
+}
+
 int mx_mg_partition(mx_mg_t mg, double tau_c, double tau_r, mx_partition_stats *per_device) {
     if (!mg) return MX_ERR_INVALID;
     if (mg->bounds.empty()) return mg->fail(MX_ERR_STATE, "mx_mg_partition: no matrix uploaded");
-    for (int g = 0; g < mg->n; ++g) {
-        int st = mx_partition(mg->h[g], tau_c, tau_r, per_device ? per_device + g : nullptr);
-        if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+    if (tau_c < tau_r) return mg->fail(MX_ERR_TAU, "col_frac must be greater than hot_frac");
+    const bool inactive = (float)tau_c == 0.0f && (float)tau_r == 0.0f;
+    if (mg->n > 1 && !inactive && mg->local_ranking == 0) {
+        int st = mg_partition_global(mg, tau_c, tau_r, per_device);
+        if (st != MX_OK) return st;
+    } else {
+        for (int g = 0; g < mg->n; ++g) {
+            int st = mx_partition(mg->h[g], tau_c, tau_r, per_device ? per_device + g : nullptr);
+            if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+        }
     }
     mg->ready = true;
+    return MX_OK;
+}
+
+int mx_mg_set_local_ranking(mx_mg_t mg, int on) {
+    if (!mg) return MX_ERR_INVALID;
+    mg->local_ranking = on ? 1 : 0;
     return MX_OK;
 }
 

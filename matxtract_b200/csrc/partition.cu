@@ -339,11 +339,29 @@ cudaError_t tiles_from_dd_t(int dRows, int nnzRowD, const int *rowPtr_dd, const 
     return cudaSuccess;
 }
 
+// rows that are hot under a GLOBAL row cut: count above the cut's, or equal and not after the cut's row
+__global__ void k_count_hot_global(const int *__restrict__ rowCntD, int n_rows, int cutCount, long long cutRow,
+                                   long long rowOffset, int *__restrict__ out) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    bool hot = false;
+    if (r < n_rows) {
+        const int c = rowCntD[r];
+        hot = c > cutCount || (c == cutCount && rowOffset + r <= cutRow);
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, hot);
+    if ((threadIdx.x & 31) == 0 && m) atomicAdd(out, __popc(m));
+}
+
+// G (may be null): the rankings of a matrix whose rows are spread over several GPUs.  col_counts = column counts of
+// the WHOLE matrix, nnz = its non-zero count (the tau thresholds are fractions of it); with has_row_cut the hot rows
+// are those above the whole matrix's row cut.  rows_only_out: stop after the per-row counts inside the hot columns and
+// copy them there (what the caller all-gathers to find the global row cut).
 template <typename V, typename B>
 cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st, int *status,
-                        cudaStream_t s) {
+                        cudaStream_t s, const GlobalRanking *G, int *rows_only_out) {
     *status = MX_OK;
     const int R = A.n_rows, C = A.n_cols, nnz = A.nnz;
+    const int nnzCut = G ? (int)G->nnz : nnz;  // what the tau fractions refer to
     TempBuf tmp;
     Scratch sc(s);
     int *colCnt = nullptr, *iota = nullptr, *sortedCnt = nullptr, *colOrder = nullptr, *pref = nullptr, *cut = nullptr,
@@ -359,23 +377,31 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     PCK(sc.alloc(&pref, (size_t)N));
     PCK(sc.alloc(&cut, 2));
     // 1-3: column histogram, ranking, tau_c cut
-    PCK(cudaMemsetAsync(colCnt, 0, (size_t)C * sizeof(int), s));
-    if (nnz > 0) k_col_hist<<<std::min(nblk(nnz), 148 * 16), 256, 0, s>>>(A.col_ind, nnz, colCnt);
+    if (G && G->col_counts) {
+        PCK(cudaMemcpyAsync(colCnt, G->col_counts, (size_t)C * sizeof(int), cudaMemcpyDeviceToDevice, s));
+    } else {
+        PCK(cudaMemsetAsync(colCnt, 0, (size_t)C * sizeof(int), s));
+        if (nnz > 0) k_col_hist<<<std::min(nblk(nnz), 148 * 16), 256, 0, s>>>(A.col_ind, nnz, colCnt);
+    }
     k_iota<<<nblk(N), 256, 0, s>>>(iota, N);
     PCK(sort_desc_pairs(tmp, colCnt, sortedCnt, iota, colOrder, C, s));
     PCK(inclusive_sum(tmp, sortedCnt, pref, C, s));
-    const int dColsNnz = nnz * tau_c;  // int * float -> float product, truncated (reference :1131)
+    const int dColsNnz = nnzCut * tau_c;  // int * float -> float product, truncated (reference :1131)
     int hcut[2] = {0, 0};
     PCK(cudaMemsetAsync(cut, 0, 2 * sizeof(int), s));
-    k_find_cut<<<nblk(std::min(R, C)), 256, 0, s>>>(pref, std::min(R, C), dColsNnz, cut);
+    // the reference scans the first rowA ranked columns (square matrix); a slab ranked on its own scans min(rows,
+    // cols), a slab ranked with the whole matrix's counts scans like the whole (square) matrix
+    const int colBound = G ? C : std::min(R, C);
+    k_find_cut<<<nblk(colBound), 256, 0, s>>>(pref, colBound, dColsNnz, cut);
     PCK(cudaMemcpyAsync(hcut, cut, 2 * sizeof(int), cudaMemcpyDeviceToHost, s));
     PCK(cudaStreamSynchronize(s));
-    const int dCols = hcut[0], nnzColD = hcut[1];
+    const int dCols = hcut[0];
+    int nnzColD = hcut[1];  // with global counts: of the whole matrix; the local figure follows from the row counts
     if (dCols == 0) {
         *status = MX_ERR_TAU;
         return cudaSuccess;
     }
-    const int sCols = C - dCols, nnzColS = nnz - nnzColD;
+    const int sCols = C - dCols;
     // 4: column map
     PCK(sc.alloc(&rankOf, (size_t)C));
     PCK(sc.alloc(&isS, (size_t)C));
@@ -391,18 +417,44 @@ cudaError_t partition_t(const CsrDev &A, float tau_c, float tau_r, PartArrays &P
     PCK(sc.alloc(&sortedRCnt, (size_t)R));
     PCK(sc.alloc(&rowOrder, (size_t)R));
     k_row_count_d<<<nblk((long long)R * 32), 256, 0, s>>>(A.row_ptr, A.col_ind, colMap, dCols, R, rowCntD);
+    if (rows_only_out) {
+        PCK(cudaMemcpyAsync(rows_only_out, rowCntD, (size_t)R * sizeof(int), cudaMemcpyDeviceToDevice, s));
+        PCK(cudaStreamSynchronize(s));
+        cudaFreeAsync(P.xperm, s);
+        P.xperm = nullptr;
+        return cudaSuccess;
+    }
     PCK(sort_desc_pairs(tmp, rowCntD, sortedRCnt, iota, rowOrder, R, s));
     PCK(inclusive_sum(tmp, sortedRCnt, pref, R, s));
-    const int dRowsNnz = nnz * tau_r;  // fraction of the TOTAL nnz (reference :1249)
-    PCK(cudaMemsetAsync(cut, 0, 2 * sizeof(int), s));
-    k_find_cut<<<nblk(R), 256, 0, s>>>(pref, R, dRowsNnz, cut);
-    PCK(cudaMemcpyAsync(hcut, cut, 2 * sizeof(int), cudaMemcpyDeviceToHost, s));
-    PCK(cudaStreamSynchronize(s));
-    const int dRows = hcut[0], nnzRowD = hcut[1];
+    if (G) {  // entries of THIS slab inside the hot columns
+        if (R > 0) PCK(cudaMemcpyAsync(&nnzColD, pref + R - 1, sizeof(int), cudaMemcpyDeviceToHost, s));
+        else nnzColD = 0;
+    }
+    int dRows = 0, nnzRowD = 0;
+    if (G && G->has_row_cut) {
+        // the whole matrix's ranking restricted to this slab is this slab's own ranking, so its hot rows are a prefix
+        // of the local order: count them (at least one row, like the reference's cut)
+        PCK(cudaMemsetAsync(cut, 0, 2 * sizeof(int), s));
+        k_count_hot_global<<<nblk(std::max(R, 1)), 256, 0, s>>>(rowCntD, R, G->row_cut_count, G->row_cut_index,
+                                                                 G->row_offset, cut);
+        PCK(cudaMemcpyAsync(hcut, cut, sizeof(int), cudaMemcpyDeviceToHost, s));
+        PCK(cudaStreamSynchronize(s));
+        dRows = std::max(1, std::min(hcut[0], R));
+        PCK(cudaMemcpyAsync(&nnzRowD, pref + dRows - 1, sizeof(int), cudaMemcpyDeviceToHost, s));
+        PCK(cudaStreamSynchronize(s));
+    } else {
+        const int dRowsNnz = nnzCut * tau_r;  // fraction of the TOTAL nnz (reference :1249)
+        PCK(cudaMemsetAsync(cut, 0, 2 * sizeof(int), s));
+        k_find_cut<<<nblk(R), 256, 0, s>>>(pref, R, dRowsNnz, cut);
+        PCK(cudaMemcpyAsync(hcut, cut, 2 * sizeof(int), cudaMemcpyDeviceToHost, s));
+        PCK(cudaStreamSynchronize(s));
+        dRows = hcut[0], nnzRowD = hcut[1];
+    }
     if (dRows == 0) {
         *status = MX_ERR_TAU;
         return cudaSuccess;
     }
+    const int nnzColS = nnz - nnzColD;
     const int sRows = R - dRows, nnzRowS = nnzColD - nnzRowD, nnzCD = nnzColS + nnzRowS;
     PCK(sc.alloc(&hotPos, (size_t)R));
     PCK(dalloc(&P.rId, (size_t)dRows, s));
@@ -474,9 +526,54 @@ int fragment_count_status(long long total_frags, int K) {
 }
 
 cudaError_t partition_run(int dtype, const CsrDev &A, float tau_c, float tau_r, PartArrays &P, mx_partition_stats &st,
-                          int *status, cudaStream_t s) {
-    if (dtype == MX_FP64) return partition_t<double, uint32_t>(A, tau_c, tau_r, P, st, status, s);
-    return partition_t<__half, uint64_t>(A, tau_c, tau_r, P, st, status, s);
+                          int *status, cudaStream_t s, const GlobalRanking *G) {
+    if (dtype == MX_FP64) return partition_t<double, uint32_t>(A, tau_c, tau_r, P, st, status, s, G, nullptr);
+    return partition_t<__half, uint64_t>(A, tau_c, tau_r, P, st, status, s, G, nullptr);
+}
+
+cudaError_t partition_row_counts(int dtype, const CsrDev &A, float tau_c, const GlobalRanking *G, int *row_counts,
+                                 int *status, cudaStream_t s) {
+    PartArrays P;
+    mx_partition_stats st{};
+    if (dtype == MX_FP64) return partition_t<double, uint32_t>(A, tau_c, 0.f, P, st, status, s, G, row_counts);
+    return partition_t<__half, uint64_t>(A, tau_c, 0.f, P, st, status, s, G, row_counts);
+}
+
+cudaError_t column_counts(const CsrDev &A, int *counts, cudaStream_t s) {
+    PCK(cudaMemsetAsync(counts, 0, (size_t)A.n_cols * sizeof(int), s));
+    if (A.nnz > 0) k_col_hist<<<std::min(nblk(A.nnz), 148 * 16), 256, 0, s>>>(A.col_ind, A.nnz, counts);
+    return cudaGetLastError();
+}
+
+// The cut of a ranking: counts sorted descending (ties: lower index first), k = smallest prefix whose sum reaches
+// `threshold` (at least 1); out = {k, prefix sum, count of the k-th element, index of the k-th element}; k = 0 when no
+// prefix reaches it.
+cudaError_t rank_cut(const int *counts, int n, int threshold, long long out[4], cudaStream_t s) {
+    out[0] = out[1] = out[2] = out[3] = 0;
+    if (n <= 0) return cudaSuccess;
+    TempBuf tmp;
+    Scratch sc(s);
+    int *iota = nullptr, *sorted = nullptr, *order = nullptr, *pref = nullptr, *cut = nullptr;
+    PCK(sc.alloc(&iota, (size_t)n));
+    PCK(sc.alloc(&sorted, (size_t)n));
+    PCK(sc.alloc(&order, (size_t)n));
+    PCK(sc.alloc(&pref, (size_t)n));
+    PCK(sc.alloc(&cut, 2));
+    k_iota<<<nblk(n), 256, 0, s>>>(iota, n);
+    PCK(sort_desc_pairs(tmp, counts, sorted, iota, order, n, s));
+    PCK(inclusive_sum(tmp, sorted, pref, n, s));
+    PCK(cudaMemsetAsync(cut, 0, 2 * sizeof(int), s));
+    k_find_cut<<<nblk(n), 256, 0, s>>>(pref, n, threshold, cut);
+    int hcut[2] = {0, 0};
+    PCK(cudaMemcpyAsync(hcut, cut, 2 * sizeof(int), cudaMemcpyDeviceToHost, s));
+    PCK(cudaStreamSynchronize(s));
+    if (hcut[0] == 0) return cudaSuccess;
+    int c = 0, idx = 0;
+    PCK(cudaMemcpyAsync(&c, sorted + hcut[0] - 1, sizeof(int), cudaMemcpyDeviceToHost, s));
+    PCK(cudaMemcpyAsync(&idx, order + hcut[0] - 1, sizeof(int), cudaMemcpyDeviceToHost, s));
+    PCK(cudaStreamSynchronize(s));
+    out[0] = hcut[0], out[1] = hcut[1], out[2] = c, out[3] = idx;
+    return cudaSuccess;
 }
 
 cudaError_t tiles_from_dd(int dtype, int dRows, int nnzRowD, const int *rowPtr_dd, const int *colInd_dd,

@@ -323,6 +323,22 @@ __device__ __forceinline__ void run_segment_full(const int4 sd, int s, int lane,
     }
 }
 
+// Every fragment of the matrix completely filled (block-structured matrices): one warp per work segment, no shared
+// memory, the value offset of fragment f is f * 8K.
+template <typename B, typename V, int K, typename OutT, bool ACCUM>
+__global__ void __launch_bounds__(128)
+    tile_kernel_full(const V *__restrict__ x_d, const V *__restrict__ tcVal, const int *__restrict__ AToX,
+                     const int4 *__restrict__ segDesc, int numSegs, const int *__restrict__ panelFirstSeg,
+                     typename std::conditional<sizeof(V) == 8, double, float>::type *__restrict__ partial,
+                     unsigned *__restrict__ panelCount, OutT *__restrict__ out, const int *__restrict__ row_map,
+                     int dRows) {
+    const int s = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (s >= numSegs) return;
+    const int4 sd = __ldg(segDesc + s);
+    run_segment_full<B, V, K, OutT, ACCUM>(sd, s, lane, sd.y * 8 * K, tcVal, AToX, x_d, panelFirstSeg, partial,
+                                           panelCount, out, row_map, dRows);
+}
+
 template <typename B, typename V, int K, typename OutT, bool ACCUM, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
     tile_kernel_staged(const V *__restrict__ x_d, const int *__restrict__ fragPtr, const B *__restrict__ fragBit,
@@ -335,14 +351,6 @@ __global__ void __launch_bounds__(NWARPS * 32)
     uint64_t *bar = reinterpret_cast<uint64_t *>(stage);
     const CtaDesc d = desc[blockIdx.x];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (d.full) {  // nothing to decode: no staging, values stream straight into the MMA operands
-        for (int s = d.seg0 + warp; s < d.seg1; s += NWARPS) {
-            const int4 sd = __ldg(segDesc + s);
-            run_segment_full<B, V, K, OutT, ACCUM>(sd, s, lane, d.v0 + (sd.y - d.f0) * 8 * K, tcVal, AToX, x_d,
-                                                   panelFirstSeg, partial, panelCount, out, row_map, dRows);
-        }
-        return;
-    }
     const StageLayout<B, V, K> L(d.f0, d.f1, d.v0, d.v1);
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
@@ -528,6 +536,10 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         g_tile_prefetch = 5 * sms;
     }
+    // all fragments completely filled <=> the packed values are exactly 8K per fragment
+    P.allFull = P.A.totalFrags > 0 && (long long)P.A.nvals == (long long)P.A.totalFrags * 8 * (dtype == MX_FP64 ? 4 : 8) &&
+                true;
+    P.useFull = P.allFull;
     const int STAGE_BYTES = STAGE_BYTES_TARGET;
     P.numCtas = (int)((totalBytes + STAGE_BYTES - 1) / STAGE_BYTES);
     if (P.numCtas < 1) P.numCtas = 1;
@@ -572,6 +584,28 @@ int tile_launches(const TilePlan &P) { return P.numSegs > 0 ? 1 : 0; }
 cudaError_t tile_spmv(int dtype, const TilePlan &P, const void *x_d, void *out, const int *row_map, bool out_is_acc,
                       bool accumulate, int *dev_err, cudaStream_t s) {
     if (P.numSegs <= 0) return cudaSuccess;
+    if (P.allFull && P.useFull) {  // nothing to decode anywhere: the streaming kernel
+        const dim3 fg((P.numSegs + 3) / 4), fb(128);
+#define MX_FULL(BT, VT, KK, OT, AC, AT)                                                                              \
+    tile_kernel_full<BT, VT, KK, OT, AC><<<fg, fb, 0, s>>>((const VT *)x_d, (const VT *)P.A.tcVal, P.A.AToX,         \
+                                                           (const int4 *)P.segDesc, P.numSegs, P.panelFirstSeg,      \
+                                                           (AT *)P.partial, P.panelCount, (OT *)out, row_map,        \
+                                                           P.A.dRows)
+        if (dtype == MX_FP64) {
+            if (accumulate)
+                MX_FULL(uint32_t, double, 4, double, true, double);
+            else
+                MX_FULL(uint32_t, double, 4, double, false, double);
+        } else if (out_is_acc) {
+            MX_FULL(uint64_t, __half, 8, float, false, float);
+        } else if (accumulate) {
+            MX_FULL(uint64_t, __half, 8, __half, true, float);
+        } else {
+            MX_FULL(uint64_t, __half, 8, __half, false, float);
+        }
+#undef MX_FULL
+        return cudaGetLastError();
+    }
     if (P.ctaDesc && P.stageBytes > 0 && P.stageBytes <= 200 * 1024) {
         dim3 sg(P.numCtas), sb(STAGE_WARPS * 32);
         const size_t smem = (size_t)P.stageBytes;

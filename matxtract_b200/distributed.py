@@ -50,6 +50,34 @@ def all_gather_rows(y_local, bounds, group=None):
     return torch.cat([out[g * longest: g * longest + sizes[g]] for g in range(world)])
 
 
+def partition_with_global_rankings(handle, tau, bounds, rank, nnz_total, device, group=None):
+    """Extracts this rank's slab with the rankings of the WHOLE matrix (one process per GPU): the slabs' column counts
+    are summed (all-reduce), the per-row counts inside the hot columns are gathered in row order, every rank takes the
+    same row cut, and ``mx_partition_global`` keeps the hot rows this rank owns.  Returns the slab's PartitionStats."""
+    import torch
+    import torch.distributed as dist
+
+    tau_c, tau_r = float(tau[0]), float(tau[1])
+    stream = torch.cuda.ExternalStream(handle.stream, device=device)
+    with torch.cuda.stream(stream):
+        counts = torch.zeros(handle.n_cols, dtype=torch.int32, device=device)
+        stream.synchronize()
+        handle.col_counts(counts)
+        dist.all_reduce(counts, group=group)
+        rows = torch.zeros(max(handle.n_rows, 1), dtype=torch.int32, device=device)[: handle.n_rows]
+        stream.synchronize()
+        handle.row_counts_in_hot_columns(tau_c, counts, nnz_total, rows)
+        all_rows = all_gather_rows(rows, bounds, group).contiguous()
+        stream.synchronize()
+    threshold = int(np.float32(np.int32(nnz_total)) * np.float32(tau_r))  # the reference's int * float, truncated
+    k, _, cut_count, cut_row = handle.rank_cut(all_rows, int(all_rows.numel()), threshold)
+    if k == 0:
+        from .capi import MxError
+
+        raise MxError(3, "tau_r threshold never reached by the ranking prefix")
+    return handle.partition_global(tau_c, tau_r, counts, nnz_total, cut_count, cut_row, bounds[rank])
+
+
 class PeerY:
     """Full-length y of every GPU, mapped into every other GPU (torch symmetric memory over NVLink), double-buffered.
 
@@ -96,7 +124,7 @@ class DistributedSpMV:
     """
 
     def __init__(self, dtype, n_cols, row_ptr, col_ind, val, rank, world, tau=(0.0, 0.0), device=None, balance="nnz",
-                 local_spmv=None, group=None, fused=False, dd_executor=None):
+                 local_spmv=None, group=None, fused=False, dd_executor=None, ranking="global"):
         self.rank, self.world, self.group = rank, world, group
         n = len(row_ptr) - 1
         self.bounds = nnz_balanced_bounds(row_ptr, world) if balance == "nnz" else equal_row_bounds(n, world)
@@ -116,7 +144,11 @@ class DistributedSpMV:
             self.handle.upload_csr(self.rows, n_cols, rp, ci, v)
             if dd_executor is not None:  # fix the executor of the core-dense block instead of timing the three
                 self.handle.set_dd_executor(dd_executor)
-            self.stats = self.handle.partition(*tau)
+            if world > 1 and ranking == "global" and tuple(float(t) for t in tau) != (0.0, 0.0):
+                self.stats = partition_with_global_rankings(self.handle, tau, self.bounds, rank, int(row_ptr[-1]),
+                                                            self.device, group)
+            else:
+                self.stats = self.handle.partition(*tau)
             self.stream = torch.cuda.ExternalStream(self.handle.stream, device=self.device)
             tdt = torch.float64 if dtype == 0 else torch.float16
             self._y = torch.zeros(max(self.rows, 1), dtype=tdt, device=self.device)[: self.rows]

@@ -446,3 +446,62 @@ def test_column_slab_execution_matches_the_plain_kernel():
         g.set_column_slabs(4)
     g.close()
     h.close()
+
+
+@pytest.mark.parametrize("name,n,tau,parts", [("c4", 60_000, (0.5, 0.25), 3), ("c2", 80_000, (0.46, 0.33), 2),
+                                              ("c3", 8 * 3000, (0.5, 0.5), 4), ("c5", 90_000, (0.7, 0.5), 5)])
+def test_slabs_extracted_with_global_rankings_reproduce_the_whole_partition(name, n, tau, parts):
+    """A matrix cut into row slabs (one handle per slab, as on several GPUs) and extracted with the WHOLE matrix's
+    column and row rankings: every slab has the whole matrix's hot columns in the same order (same dCols, same xperm),
+    the slabs' hot rows together are exactly the whole matrix's hot rows, and the slabs' products concatenate to y."""
+    import torch
+    from matxtract_b200.distributed import nnz_balanced_bounds, slab
+
+    m = synth.generate(name, n=n)
+    dtype, rp, ci, val, x = m["dtype"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    nnz = m["nnz"]
+    whole = mx.MatXtract(dtype)
+    whole.upload_csr(n, n, rp, ci, val)
+    sw = whole.partition(*tau)
+    dw = whole.download_partition()
+    bounds = nnz_balanced_bounds(rp, parts)
+    hs = []
+    total = torch.zeros(n, dtype=torch.int32, device="cuda")
+    for g in range(parts):
+        r0, r1 = bounds[g], bounds[g + 1]
+        h = mx.MatXtract(dtype)
+        h.upload_csr(r1 - r0, n, *slab(rp, ci, val, r0, r1))
+        c = torch.zeros(n, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        h.col_counts(c)
+        total += c
+        hs.append(h)
+    torch.cuda.synchronize()
+    rows = torch.zeros(n, dtype=torch.int32, device="cuda")
+    for g, h in enumerate(hs):
+        part = torch.zeros(max(h.n_rows, 1), dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        h.row_counts_in_hot_columns(tau[0], total, nnz, part)
+        rows[bounds[g]:bounds[g + 1]] = part[: h.n_rows]
+    torch.cuda.synchronize()
+    k, s, cut_count, cut_row = hs[0].rank_cut(rows, n, int(np.float32(np.int32(nnz)) * np.float32(tau[1])))
+    assert (k, s) == (sw.dRows, sw.nnzRowD)
+    hot, y = [], []
+    for g, h in enumerate(hs):
+        st = h.partition_global(tau[0], tau[1], total, nnz, cut_count, cut_row, bounds[g])
+        d = h.download_partition()
+        assert st.dCols == sw.dCols
+        np.testing.assert_array_equal(d["xperm"], dw["xperm"])
+        hot.append(d["rId"].astype(np.int64) + bounds[g])
+        assert st.nnzRowD + st.nnzCD == h.nnz
+        y.append(h.spmv_host(x))
+        assert h.device_error() == 0
+    hot = np.concatenate(hot)
+    owners_without_hot_rows = sum(1 for g in range(parts)
+                                  if not ((dw["rId"] >= bounds[g]) & (dw["rId"] < bounds[g + 1])).any())
+    # a slab that owns none of the hot rows still extracts one row (the reference's cut is never empty)
+    assert len(hot) == sw.dRows + owners_without_hot_rows
+    assert set(dw["rId"].tolist()) <= set(hot.tolist())
+    check_y(dtype, np.concatenate(y), rp, ci, val, x)
+    for h in hs + [whole]:
+        h.close()
