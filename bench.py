@@ -388,9 +388,18 @@ def run_ours(args):
     h = mx.MatXtract(dtype, device=local)
     # rows [r0, r1) x all n_total columns, extracted on its own
     h.upload_csr(n_local, n_total, m["row_ptr"], m["col_ind"], m["val"])
-    st = h.partition(*tau)
+    global_ranking = world > 1 and tuple(float(t) for t in tau) != (0.0, 0.0) and args.ranking == "global"
+
+    def extract():
+        if global_ranking:  # the whole matrix's column and row rankings: counts summed / gathered over the ranks
+            from matxtract_b200.distributed import partition_with_global_rankings
+
+            return partition_with_global_rankings(h, tau, bounds, rank, nnz_total, dev)
+        return h.partition(*tau)
+
+    st = extract()
     preprocess_ms_cold = st.preprocess_ms  # first call: includes CUDA module loading and memory-pool growth
-    st = h.partition(*tau)                 # steady-state cost of the same extraction
+    st = extract()                         # steady-state cost of the same extraction
     dd_times = h.dd_executor_times
     if args.dd != "auto":
         h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR, "se": mx.DD_SE}[args.dd])
@@ -711,7 +720,9 @@ def run_ours(args):
         "effective_gbs": eff_gbs, "pct_of_8tbs": 100.0 * eff_gbs / NOMINAL_HBM_GBS / world,
         "pct_of_measured_hbm": 100.0 * eff_gbs / peak / world,
         "algorithmic_bytes_per_step": b_alg_total,
-        "partition": {k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
+        "partition": {**{k: getattr(st, k) for k in ("active", "dCols", "dRows", "nnzRowD", "nnzCD", "totalFrags", "fragK")},
+                      "ranking": "whole matrix (counts exchanged between the GPUs)" if global_ranking else
+                      ("per slab" if world > 1 and st.active else "single matrix")},
         "dd_executor": {1: "tile (tensor cores)", 2: "csr (CUDA cores)", 3: "sparse-encode (tensor cores)"}.get(
             h.dd_executor, "none"),
         "dd_executor_tuned_ms": {"tile": dd_times[0], "csr": dd_times[1], "sparse_encode": dd_times[2]},
@@ -761,6 +772,8 @@ def main():
                     help="N > 1: how y is assembled (auto = the fastest of epilogue / push / nccl, timed at set-up)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the one matrix cut into N slabs (default), weak = N times the rows")
+    ap.add_argument("--ranking", default="global", choices=["global", "local"],
+                    help="N > 1, tau != (0,0): rank columns and rows over the whole matrix (default) or per slab")
     ap.add_argument("--dd", default="auto", choices=["auto", "tile", "csr", "se"],
                     help="executor of the core-dense block (auto = the fastest of the three, timed at partition time)")
     ap.add_argument("--colspace", default="auto", choices=["auto", "permuted", "original"],

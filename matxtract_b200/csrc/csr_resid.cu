@@ -401,10 +401,16 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
         atomicOr(&sFlag[e1 >> 5], 1u << (e1 & 31));
         atomicMin(&sFirst[e1 >> 5], tid + THREADS);
     }
-    for (int k = tid + 2 * THREADS; k < nEmit; k += THREADS) {
-        const int e = __ldg(ce + 1 + k) - base - 1;
-        atomicOr(&sFlag[e >> 5], 1u << (e & 31));
-        atomicMin(&sFirst[e >> 5], k);
+    for (int k0 = tid + 2 * THREADS; k0 < nEmit; k0 += 4 * THREADS) {  // further row ends, four loads in flight
+        int e[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) e[j] = k0 + j * THREADS < nEmit ? __ldg(ce + 1 + k0 + j * THREADS) - base - 1 : -1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (e[j] >= 0) {
+                atomicOr(&sFlag[e[j] >> 5], 1u << (e[j] & 31));
+                atomicMin(&sFirst[e[j] >> 5], k0 + j * THREADS);
+            }
     }
     tile_sync<GROUPS>(grp);
 
@@ -520,10 +526,52 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
             return;
         }
     }
-    if (q0 < nEmit) store_row<V, HAS_TILE, MODE>(out, rz, ysum[q0]);
-    for (int q = q0 + THREADS; q < nEmit; q += THREADS) {
-        const int r = out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q;
-        store_row<V, HAS_TILE, MODE>(out, r, ysum[q]);
+    // One row per thread per round, EB rounds batched: the row indices of a batch are requested together, then
+    // everything that depends on them (old y when accumulating, the tile half's carrier, the carrier's destination),
+    // then the stores - three dependent round trips per batch instead of per round.  A tile of short rows closes many
+    // rows (a column-slab pass: ~700), and one round at a time left the kernel waiting on these chains.
+    constexpr int EB = 4;
+    for (int qs = q0; qs < nEmit; qs += EB * THREADS) {
+        int r[EB], dst[EB];
+        A add[EB];
+#pragma unroll
+        for (int k = 0; k < EB; ++k) {
+            const int q = qs + k * THREADS;
+            r[k] = q < nEmit ? (q == q0 ? rz : (out.nzRow ? __ldg(out.nzRow + r0 + q) : r0 + q)) : -1;
+        }
+#pragma unroll
+        for (int k = 0; k < EB; ++k) {
+            dst[k] = r[k];
+            add[k] = A(0);
+            if (r[k] >= 0) {
+                if (MODE == OUT_CARRIER) {
+                    dst[k] = __ldg(out.row_map + r[k]);
+                } else {
+                    if (HAS_TILE) {
+                        if ((__ldg(out.hotmask + (r[k] >> 5)) >> (r[k] & 31)) & 1u) add[k] = out.ytile[r[k]];
+                    }
+                    if (MODE == OUT_Y_ACCUM) add[k] += to_acc(out.y[r[k]]);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < EB; ++k) {
+            if (r[k] < 0) continue;
+            const A v = ysum[qs + k * THREADS] + add[k];
+            if (MODE == OUT_CARRIER) {
+                out.carrier_out[dst[k]] = v;
+            } else if (MODE == OUT_Y_PEERS) {
+                if constexpr (sizeof(V) == 8) {
+                    if (out.multicast()) {
+                        multicast_store64(reinterpret_cast<double *>(out.multicast()) + out.row_offset + r[k], v);
+                        continue;
+                    }
+                }
+                store_peers<V>(out, r[k], v);
+            } else {
+                from_acc(v, out.y + r[k]);
+            }
+        }
     }
 }
 
