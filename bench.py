@@ -127,6 +127,10 @@ def workload_shape(args, world):
     from matxtract_b200 import synth
 
     cfg = synth.CONFIGS[args.workload]
+    if getattr(args, "dtype", None):  # the same shape in the other value type
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, dtype={"f64": 0, "f16": 1}[args.dtype])
     n_total = (args.n or cfg.n) * (world if args.scaling == "weak" else 1)
     if cfg.kind == synth.BLOCK:
         n_total -= n_total % 8
@@ -768,6 +772,8 @@ def main():
     ap.add_argument("--n", "--rows", dest="n", type=int, default=0,
                     help="rows of the matrix (default: the configuration's size); spell it --rows under torchrun")
     ap.add_argument("--tau", type=float, nargs=2, default=None)
+    ap.add_argument("--dtype", default=None, choices=["f64", "f16"],
+                    help="value type (default: the configuration's own)")
     ap.add_argument("--gather", default="auto", choices=["auto", "epilogue", "multicast", "push", "nccl"],
                     help="N > 1: how y is assembled (auto = the fastest of epilogue / push / nccl, timed at set-up)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],

@@ -117,8 +117,8 @@ int mx_load_partition(mx_handle_t h, const char *path, mx_partition_stats *stats
 int mx_check_partition_file(const char *path, int dtype, char *msg, int msg_len);
 
 /* Searches (tau_c, tau_r) on the device instead of the reference's 20-run Bayesian search through the command-line
- * driver (ML/bayes_opt.py:153-163): every valid point of the grid {0, 1/grid, ..., (grid-1)/grid}^2 with
- * tau_c >= tau_r is extracted and its product timed (3 warm + 10 timed); the fastest is left installed in the handle.
+ * driver (ML/bayes_opt.py:153-163): every valid point of the grid {0, 1/grid, ..., 1}^2 with tau_c >= tau_r is
+ * extracted and its product timed (3 warm + 10 timed); the fastest is left installed in the handle.
  * ms_plain is the time of tau = (0,0). */
 int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float *ms_best, float *ms_plain);
 

@@ -852,7 +852,7 @@ int mx_autotune_tau(mx_handle_t h, int grid, double *tau_c, double *tau_r, float
     const cudaEvent_t e0 = ev.e0, e1 = ev.e1;
     double bc = 0, br = 0;
     float best = -1.f, plain = 0.f;
-    for (int i = 0; i < grid; ++i)
+    for (int i = 0; i <= grid; ++i)  // tau_c = i / grid up to 1 (everything in the core-dense block's columns)
         for (int j = 0; j <= i; ++j) {
             if (i == 0 && j > 0) continue;
             const double tc = (double)i / grid, tr = (double)j / grid;
