@@ -392,6 +392,7 @@ def run_ours(args):
     h = mx.MatXtract(dtype, device=local)
     # rows [r0, r1) x all n_total columns, extracted on its own
     h.upload_csr(n_local, n_total, m["row_ptr"], m["col_ind"], m["val"])
+    h.set_row_offset(r0)
     global_ranking = world > 1 and tuple(float(t) for t in tau) != (0.0, 0.0) and args.ranking == "global"
 
     def extract():

@@ -278,14 +278,18 @@ enum { MX_HOT_AUTO = 0, MX_HOT_OFF = 1, MX_HOT_ON = 2 };
 int mx_set_hot_prefix(mx_handle_t h, int mode);
 int mx_hot_prefix(mx_handle_t h, int *hot_cols, float *ms_with, float *ms_without);
 /* Column-slab execution of the plain CSR product (tau = (0,0)) for a matrix whose x is far larger than the L2 cache.
- * A CSR-ordered kernel then pays one 64-byte DRAM burst per gathered x value; cut into vertical slabs, each stored as
- * its own CSR over its non-empty rows and multiplied in a pass that adds into y, the gathers of a pass stay inside a
- * 32 MB range of x that L2 holds.  count = -1 (default): when x exceeds L2, mx_partition builds the slabs, times the
- * product both ways and keeps the faster; 0 = never; k >= 2 = always k slabs.  FP64 only (the passes accumulate in
- * the value type); rows must have ascending column ids (otherwise the plain kernel stays).  mx_column_slabs reports
- * the slab count in use (0 = plain kernel) and the two timings.  With slabs, mx_spmv_peers accumulates this GPU's
- * rows in its own buffer and then pushes them to the peers.  The reference has one CSR kernel over the whole matrix
- * (src/spmv_kernel/cdSpMV.cu:395-491). */
+ * A CSR-ordered kernel then pays one 64-byte DRAM burst per gathered x value.  The matrix is split into its BAND (the
+ * entries within 65,536 columns of the diagonal: one CSR pass over all rows, whose gathers walk x almost
+ * sequentially) and its FAR entries, cut into vertical slabs, each stored as its own CSR over its non-empty rows and
+ * multiplied in a pass that adds into y while gathering from an x range that L2 holds.  count = -1 (default): when x
+ * exceeds L2, mx_partition builds the slabs for x ranges of 96 / 64 / 32 MB, times the product each way and keeps the
+ * fastest; 0 = never; k >= 2 = always k slabs.  FP64 only (the passes accumulate in the value type); rows must have
+ * ascending column ids (otherwise the plain kernel stays).  mx_column_slabs reports the slab count in use (0 = plain
+ * kernel) and the timings.  For a row slab of a larger square matrix, mx_set_row_offset (before mx_partition) tells
+ * where its diagonal lies; mx_spmv_peers then runs the far passes first, accumulating locally, and the band pass
+ * last, storing the finished rows into every GPU's y from its epilogue.  The reference has one CSR kernel over the
+ * whole matrix (src/spmv_kernel/cdSpMV.cu:395-491). */
+int mx_set_row_offset(mx_handle_t h, long long first_global_row);
 int mx_set_column_slabs(mx_handle_t h, int count);
 int mx_column_slabs(mx_handle_t h, int *count, float *ms_plain, float *ms_slabbed);
 /* Number of kernel launches one mx_spmv issues for the current matrix / partition. */

@@ -113,6 +113,7 @@ SYMBOLS = {
     "mx_set_column_space": (_i, [_vp, _i]),
     "mx_column_space": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_set_column_slabs": (_i, [_vp, _i]),
+    "mx_set_row_offset": (_i, [_vp, C.c_longlong]),
     "mx_column_slabs": (_i, [_vp, _ip, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mx_set_hot_prefix": (_i, [_vp, _i]),
     "mx_hot_prefix": (_i, [_vp, _ip, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
@@ -348,6 +349,10 @@ class MatXtract:
         a, b = C.c_float(), C.c_float()
         m = lib().mx_column_space(self._h, C.byref(a), C.byref(b))
         return m, a.value, b.value
+
+    def set_row_offset(self, first_global_row: int):
+        """Where this handle's row slab sits in the whole square matrix (before partition; places the band)."""
+        self._ck(lib().mx_set_row_offset(self._h, int(first_global_row)))
 
     def set_column_slabs(self, count: int):
         """-1 = automatic (when x exceeds L2, timed), 0 = off, k >= 2 = k column slabs (tau = (0,0), FP64)."""

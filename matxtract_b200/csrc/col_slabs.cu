@@ -3,10 +3,16 @@
 // A CSR-ordered kernel gathers x[col] for every non-zero.  When x is much larger than L2 (a 64M-column FP64 vector is
 // 512 MB) and the columns of a row are spread over the whole range, every such gather is a DRAM access that moves a
 // whole 64-byte burst for 8 useful bytes: measured on the 1e9-non-zero power-law matrix, the kernel moves 3-4x the
-// matrix's own bytes.  Here the matrix is cut into vertical slabs of `width` columns, each stored as its own CSR over
-// its non-empty rows.  One pass per slab streams that slab's entries and gathers from a 32 MB range of x that stays in
-// L2; the price is that y is read and written once per pass instead of once.  The passes are the ordinary CSR kernel
-// (resid_kernel) in its accumulate mode, so the arithmetic stays free of atomics and bit-reproducible.
+// matrix's own bytes.  Here the matrix is split in two:
+//   * the BAND: the entries of every row whose column lies within COL_SLAB_HALO of the row's own index.  Their
+//     gathers walk x almost sequentially whatever its size, so the band is one ordinary CSR pass over all rows;
+//   * the FAR entries, cut into vertical slabs of `width` columns, each stored as its own CSR over its non-empty
+//     rows.  One pass per slab streams that slab's entries and gathers from an x range that stays in L2; the price
+//     is that the rows a pass touches are read and written once per pass.
+// All passes are the ordinary CSR kernel (resid_kernel), the far ones in its accumulate mode, so the arithmetic stays
+// free of atomics and bit-reproducible.  On one GPU the band pass runs first and writes every row; as one GPU's share
+// of a row-partitioned matrix it runs LAST and stores the finished rows into every GPU's y from its epilogue, so that
+// the exchange overlaps the pass that holds about half of the work.
 // The reference has no counterpart: it runs one CSR kernel over the whole matrix (src/spmv_kernel/cdSpMV.cu:395-491).
 #include <algorithm>
 
@@ -23,6 +29,8 @@ namespace {
     } while (0)
 
 inline int nblk(long long n, int b = 256) { return (int)((n + b - 1) / b); }
+
+constexpr int COL_SLAB_HALO = 1 << 16;  // columns on either side of the diagonal that count as the band
 
 // first position in [lo, hi) whose column is >= c
 __device__ __forceinline__ int lower_col(const int *__restrict__ col, int lo, int hi, int c) {
@@ -44,41 +52,50 @@ __global__ void k_rows_sorted(const int *__restrict__ row_ptr, const int *__rest
     if (__any_sync(0xffffffffu, b) && lane == 0) *bad = 1;
 }
 
-// the part of every row that falls into columns [c0, c1): start in the source arrays, length, non-empty flag
-__global__ void k_slab_ranges(const int *__restrict__ row_ptr, const int *__restrict__ col, int n, int c0, int c1,
-                              int *__restrict__ lo, int *__restrict__ len, int *__restrict__ flag) {
+// the band of every row: entries whose column lies within `halo` of the row's own (global) index
+__global__ void k_near_ranges(const int *__restrict__ row_ptr, const int *__restrict__ col, int n, long long row_offset,
+                              int halo, int *__restrict__ nlo, int *__restrict__ nlen) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r > n) return;
     int a = 0, l = 0;
     if (r < n) {
         const int b = row_ptr[r], e = row_ptr[r + 1];
-        a = lower_col(col, b, e, c0);
-        l = lower_col(col, a, e, c1) - a;
+        const long long g = row_offset + r;
+        const long long c0 = g - halo, c1 = g + halo + 1;  // [c0, c1)
+        a = lower_col(col, b, e, (int)max(c0, 0LL));
+        l = lower_col(col, a, e, (int)min(c1, 2147483647LL)) - a;
     }
-    lo[r] = a;
-    len[r] = l;
-    flag[r] = l > 0;
+    nlo[r] = a;
+    nlen[r] = l;
 }
 
-// one warp per 32 rows: every lane owns a row; short parts are copied by their lane, long ones by the whole warp
-template <typename V>
-__global__ void k_slab_copy(const int *__restrict__ col, const V *__restrict__ val, const int *__restrict__ lo,
-                            const int *__restrict__ len, const int *__restrict__ pos, const int *__restrict__ off, int n,
-                            int m_rows, int nnz_slab, int *__restrict__ c_ptr, int *__restrict__ nz_row,
-                            int *__restrict__ ocol, V *__restrict__ oval) {
-    const int r = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31;
-    int a = 0, l = 0, o = 0;
+// the part of every row that falls into columns [c0, c1) and is NOT in the row's band: at most two ranges of the
+// (sorted) row, [lo1, lo1 + len1) left of the band and [lo2, lo2 + len2) right of it
+__global__ void k_far_ranges(const int *__restrict__ row_ptr, const int *__restrict__ col, const int *__restrict__ nlo,
+                             const int *__restrict__ nlen, int n, int c0, int c1, int *__restrict__ lo1,
+                             int *__restrict__ len1, int *__restrict__ lo2, int *__restrict__ len2,
+                             int *__restrict__ len, int *__restrict__ flag) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r > n) return;
+    int a1 = 0, l1 = 0, a2 = 0, l2 = 0;
     if (r < n) {
-        a = lo[r];
-        l = len[r];
-        o = off[r];
-        if (l > 0) {
-            const int k = pos[r];
-            c_ptr[k] = o;
-            nz_row[k] = r;
-        }
+        const int b = row_ptr[r], e = row_ptr[r + 1];
+        const int p0 = lower_col(col, b, e, c0), p1 = lower_col(col, p0, e, c1);
+        const int w0 = nlo[r], w1 = w0 + nlen[r];
+        a1 = p0;
+        l1 = max(0, min(p1, w0) - p0);
+        a2 = max(p0, w1);
+        l2 = max(0, p1 - a2);
     }
-    if (r == 0) c_ptr[m_rows] = nnz_slab;
+    lo1[r] = a1, len1[r] = l1, lo2[r] = a2, len2[r] = l2;
+    len[r] = l1 + l2;
+    flag[r] = l1 + l2 > 0;
+}
+
+// copies entries [a, a + l) of the source arrays to [o, o + l): short ranges by their lane, long ones by the warp
+template <typename V>
+__device__ __forceinline__ void copy_ranges(const int *__restrict__ col, const V *__restrict__ val, int a, int l, int o,
+                                            int lane, int *__restrict__ ocol, V *__restrict__ oval) {
     if (l > 0 && l < 32)
         for (int j = 0; j < l; ++j) {
             ocol[o + j] = __ldg(col + a + j);
@@ -97,21 +114,56 @@ __global__ void k_slab_copy(const int *__restrict__ col, const V *__restrict__ v
     }
 }
 
+// one lane per row (a warp per 32 rows): the row's band -> the near matrix (row pointers = off)
 template <typename V>
-cudaError_t build_t(const CsrDev &A, int count, ColSlabs &out, int *status, cudaStream_t s) {
+__global__ void k_near_copy(const int *__restrict__ col, const V *__restrict__ val, const int *__restrict__ nlo,
+                            const int *__restrict__ nlen, const int *__restrict__ off, int n, int *__restrict__ ocol,
+                            V *__restrict__ oval) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31;
+    int a = 0, l = 0, o = 0;
+    if (r < n) a = nlo[r], l = nlen[r], o = off[r];
+    copy_ranges<V>(col, val, a, l, o, lane, ocol, oval);
+}
+
+// one lane per row: the row's far entries inside the slab -> the slab's CSR over its non-empty rows
+template <typename V>
+__global__ void k_far_copy(const int *__restrict__ col, const V *__restrict__ val, const int *__restrict__ lo1,
+                           const int *__restrict__ len1, const int *__restrict__ lo2, const int *__restrict__ len2,
+                           const int *__restrict__ pos, const int *__restrict__ off, int n, int m_rows, int nnz_slab,
+                           int *__restrict__ c_ptr, int *__restrict__ nz_row, int *__restrict__ ocol,
+                           V *__restrict__ oval) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31;
+    int a1 = 0, l1 = 0, a2 = 0, l2 = 0, o = 0;
+    if (r < n) {
+        a1 = lo1[r], l1 = len1[r], a2 = lo2[r], l2 = len2[r], o = off[r];
+        if (l1 + l2 > 0) {
+            const int k = pos[r];
+            c_ptr[k] = o;
+            nz_row[k] = r;
+        }
+    }
+    if (r == 0) c_ptr[m_rows] = nnz_slab;
+    copy_ranges<V>(col, val, a1, l1, o, lane, ocol, oval);
+    copy_ranges<V>(col, val, a2, l2, o + l1, lane, ocol, oval);
+}
+
+template <typename V>
+cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &out, int *status, cudaStream_t s) {
+    constexpr int dtype = sizeof(V) == 8 ? MX_FP64 : MX_FP16;
     const int n = A.n_rows;
     const size_t n1 = (size_t)n + 1;
     *status = MX_OK;
     TempBuf tmp;
-    int *lo = nullptr, *len = nullptr, *flag = nullptr, *pos = nullptr, *off = nullptr, *bad = nullptr;
+    int *nlo = nullptr, *nlen = nullptr, *lo1 = nullptr, *len1 = nullptr, *lo2 = nullptr, *len2 = nullptr, *len = nullptr,
+        *flag = nullptr, *pos = nullptr, *off = nullptr, *bad = nullptr;
     struct Guard {
         cudaStream_t s;
-        int **p[6];
+        int **p[11];
         ~Guard() {
             for (int **q : p)
                 if (*q) cudaFreeAsync(*q, s);
         }
-    } guard{s, {&lo, &len, &flag, &pos, &off, &bad}};
+    } guard{s, {&nlo, &nlen, &lo1, &len1, &lo2, &len2, &len, &flag, &pos, &off, &bad}};
     CS_TRY(cudaMallocAsync(&bad, sizeof(int), s));
     CS_TRY(cudaMemsetAsync(bad, 0, sizeof(int), s));
     if (n > 0) k_rows_sorted<<<nblk((long long)n * 32), 256, 0, s>>>(A.row_ptr, A.col_ind, n, bad);
@@ -122,22 +174,42 @@ cudaError_t build_t(const CsrDev &A, int count, ColSlabs &out, int *status, cuda
         *status = MX_ERR_INVALID;
         return cudaSuccess;
     }
-    CS_TRY(cudaMallocAsync(&lo, n1 * sizeof(int), s));
-    CS_TRY(cudaMallocAsync(&len, n1 * sizeof(int), s));
-    CS_TRY(cudaMallocAsync(&flag, n1 * sizeof(int), s));
-    CS_TRY(cudaMallocAsync(&pos, n1 * sizeof(int), s));
-    CS_TRY(cudaMallocAsync(&off, n1 * sizeof(int), s));
+    for (int **q : {&nlo, &nlen, &lo1, &len1, &lo2, &len2, &len, &flag, &pos, &off})
+        CS_TRY(cudaMallocAsync(q, n1 * sizeof(int), s));
     int width = (int)(((long long)A.n_cols + count - 1) / count);
     width = (width + 15) & ~15;
     out.count = count;
     out.width = width;
+    out.halo = COL_SLAB_HALO;
+    out.row_offset = row_offset;
     out.plans = new ResidPlan[count];
     out.col = new int *[count]();
     out.val = new void *[count]();
+    // ---- the band: a CSR over all rows ----
+    k_near_ranges<<<nblk(n1), 256, 0, s>>>(A.row_ptr, A.col_ind, n, row_offset, out.halo, nlo, nlen);
+    CS_TRY(cudaMallocAsync(&out.near_row_ptr, n1 * sizeof(int), s));
+    CS_TRY(exclusive_sum(tmp, nlen, out.near_row_ptr, (int)n1, s));
+    int nnz_near = 0;
+    CS_TRY(cudaMemcpyAsync(&nnz_near, out.near_row_ptr + n, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CS_TRY(cudaStreamSynchronize(s));
+    CS_TRY(cudaMallocAsync(&out.near_col, (size_t)std::max(nnz_near, 1) * sizeof(int), s));
+    CS_TRY(cudaMallocAsync(&out.near_val, (size_t)std::max(nnz_near, 1) * sizeof(V), s));
+    k_near_copy<V><<<nblk(std::max(n, 1)), 256, 0, s>>>(A.col_ind, (const V *)A.val, nlo, nlen, out.near_row_ptr, n,
+                                                        out.near_col, (V *)out.near_val);
+    CS_TRY(cudaGetLastError());
+    out.near.n_rows = n;
+    out.near.n_cols = A.n_cols;
+    out.near.nnz = nnz_near;
+    out.near.row_ptr = out.near_row_ptr;
+    out.near.col_ind = out.near_col;
+    out.near.val = out.near_val;
+    CS_TRY(resid_plan_build(dtype, out.near, s));
+    out.near.prefetch_tiles = 0;
+    // ---- the far entries, one slab of columns at a time ----
     for (int k = 0; k < count; ++k) {
-        const long long c0 = (long long)k * width, c1 = std::min<long long>(c0 + width, A.n_cols);
-        k_slab_ranges<<<nblk(n1), 256, 0, s>>>(A.row_ptr, A.col_ind, n, (int)std::min<long long>(c0, A.n_cols), (int)c1,
-                                               lo, len, flag);
+        const long long c0 = std::min<long long>((long long)k * width, A.n_cols), c1 = std::min<long long>(c0 + width, A.n_cols);
+        k_far_ranges<<<nblk(n1), 256, 0, s>>>(A.row_ptr, A.col_ind, nlo, nlen, n, (int)c0, (int)c1, lo1, len1, lo2, len2,
+                                              len, flag);
         CS_TRY(exclusive_sum(tmp, flag, pos, (int)n1, s));
         CS_TRY(exclusive_sum(tmp, len, off, (int)n1, s));
         int m_rows = 0, nnz_slab = 0;
@@ -152,25 +224,28 @@ cudaError_t build_t(const CsrDev &A, int count, ColSlabs &out, int *status, cuda
         P.n_empty = 0;  // rows without entries in this slab are not touched by its pass
         CS_TRY(cudaMallocAsync(&P.c_ptr_own, ((size_t)m_rows + 1) * sizeof(int), s));
         CS_TRY(cudaMallocAsync(&P.nz_row, ((size_t)m_rows + 1) * sizeof(int), s));
-        CS_TRY(cudaMallocAsync(&out.col[k], (size_t)(nnz_slab > 0 ? nnz_slab : 1) * sizeof(int), s));
-        CS_TRY(cudaMallocAsync(&out.val[k], (size_t)(nnz_slab > 0 ? nnz_slab : 1) * sizeof(V), s));
-        k_slab_copy<V><<<nblk(std::max(n, 1)), 256, 0, s>>>(A.col_ind, (const V *)A.val, lo, len, pos, off, n, m_rows,
-                                                            nnz_slab, P.c_ptr_own, P.nz_row, out.col[k], (V *)out.val[k]);
+        CS_TRY(cudaMallocAsync(&out.col[k], (size_t)std::max(nnz_slab, 1) * sizeof(int), s));
+        CS_TRY(cudaMallocAsync(&out.val[k], (size_t)std::max(nnz_slab, 1) * sizeof(V), s));
+        k_far_copy<V><<<nblk(std::max(n, 1)), 256, 0, s>>>(A.col_ind, (const V *)A.val, lo1, len1, lo2, len2, pos, off, n,
+                                                           m_rows, nnz_slab, P.c_ptr_own, P.nz_row, out.col[k],
+                                                           (V *)out.val[k]);
         CS_TRY(cudaGetLastError());
         P.c_ptr = P.c_ptr_own;
         P.row_ptr = nullptr;
         P.col_ind = out.col[k];
         P.val = out.val[k];
-        CS_TRY(resid_plan_finish(sizeof(V) == 8 ? MX_FP64 : MX_FP16, P, s));
+        CS_TRY(resid_plan_finish(dtype, P, s));
     }
     return cudaSuccess;
 }
 
 }  // namespace
 
-cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, ColSlabs &out, int *status, cudaStream_t s) {
+cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, long long row_offset, ColSlabs &out, int *status,
+                            cudaStream_t s) {
     if (count < 1) count = 1;
-    cudaError_t e = dtype == MX_FP64 ? build_t<double>(A, count, out, status, s) : build_t<__half>(A, count, out, status, s);
+    cudaError_t e = dtype == MX_FP64 ? build_t<double>(A, count, row_offset, out, status, s)
+                                     : build_t<__half>(A, count, row_offset, out, status, s);
     if (e != cudaSuccess || *status != MX_OK) col_slabs_free(out, s);
     return e;
 }
@@ -181,17 +256,44 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s) {
         if (S.col && S.col[k]) cudaFreeAsync(S.col[k], s);
         if (S.val && S.val[k]) cudaFreeAsync(S.val[k], s);
     }
+    resid_plan_free(S.near, s);
+    for (void *p : {(void *)S.near_row_ptr, (void *)S.near_col, S.near_val})
+        if (p) cudaFreeAsync(p, s);
     delete[] S.plans;
     delete[] S.col;
     delete[] S.val;
     S = ColSlabs();
 }
 
-cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s) {
-    cudaError_t e = cudaMemsetAsync(y, 0, y_bytes, s);
+int col_slabs_launches(const ColSlabs &S) {
+    int n = resid_launches(S.near);
+    for (int k = 0; k < S.count; ++k)
+        if (S.plans[k].nnz > 0) n += resid_launches(S.plans[k]);
+    return n;
+}
+
+// y = A x on one GPU: the band pass writes every row, the far passes add to it (each chained behind its predecessor:
+// its prologue overlaps the previous pass's tail).
+cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, cudaStream_t s) {
+    cudaError_t e = resid_spmv(dtype, S.near, x, y, nullptr, nullptr, /*accumulate=*/false, s);
     for (int k = 0; k < S.count && e == cudaSuccess; ++k)
-        if (S.plans[k].nnz > 0)  // passes after the first are chained: their prologue overlaps the previous pass's tail
-            e = resid_spmv(dtype, S.plans[k], x, y, nullptr, nullptr, /*accumulate=*/true, s, /*chained=*/k > 0);
+        if (S.plans[k].nnz > 0) e = resid_spmv(dtype, S.plans[k], x, y, nullptr, nullptr, /*accumulate=*/true, s, true);
+    return e;
+}
+
+// The same product as one GPU's share of a row-partitioned matrix: the far passes accumulate this GPU's rows in
+// y_own (its rows inside its own full-length buffer, cleared first); the band pass comes LAST, adds what y_own holds
+// and stores every finished row into all GPUs' buffers from its epilogue, so the exchange overlaps that pass.
+cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *y_own, size_t y_bytes,
+                                 void *const *peers, int n_peers, long long row_offset, cudaStream_t s) {
+    cudaError_t e = cudaMemsetAsync(y_own, 0, y_bytes, s);
+    bool first = true;
+    for (int k = 0; k < S.count && e == cudaSuccess; ++k)
+        if (S.plans[k].nnz > 0) {
+            e = resid_spmv(dtype, S.plans[k], x, y_own, nullptr, nullptr, /*accumulate=*/true, s, /*chained=*/!first);
+            first = false;
+        }
+    if (e == cudaSuccess) e = resid_spmv_peers_accum(dtype, S.near, x, y_own, peers, n_peers, row_offset, s, !first);
     return e;
 }
 

@@ -50,8 +50,11 @@ enum OutMode : int {
     OUT_Y = 0,        // y[r] = sum (+ tile contribution of hot rows)
     OUT_Y_ACCUM = 1,  // y[r] += sum  (the reference's cdspmv adds into y, cdSpMV.cu:418,483)
     OUT_CARRIER = 2,  // carrier[row_map[r]] = sum in the accumulate type (core-dense block run as CSR)
-    OUT_Y_PEERS = 3   // y_peer[g][row_offset + r] = sum for every GPU g of the box: the y all-gather, fused
+    OUT_Y_PEERS = 3,  // y_peer[g][row_offset + r] = sum for every GPU g of the box: the y all-gather, fused
+    OUT_Y_PEERS_ACCUM = 4  // y_peer[g][row_offset + r] = y[r] + sum: the last pass of a product made of several passes
 };
+__host__ __device__ constexpr bool is_peers(int m) { return m == OUT_Y_PEERS || m == OUT_Y_PEERS_ACCUM; }
+__host__ __device__ constexpr bool is_accum(int m) { return m == OUT_Y_ACCUM || m == OUT_Y_PEERS_ACCUM; }
 constexpr int MAX_PEERS = 8;
 constexpr int PEER_VEC_FLAG = 0x100;
 
@@ -127,7 +130,7 @@ __device__ __forceinline__ typename AccOf<V>::T row_value(const RowOut<V> &o, in
     if (HAS_TILE) {
         if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
     }
-    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
+    if (is_accum(MODE)) v += to_acc(o.y[r]);
     return v;
 }
 
@@ -203,8 +206,8 @@ __device__ __forceinline__ void store_row(const RowOut<V> &o, int r, typename Ac
     if (HAS_TILE) {
         if ((__ldg(o.hotmask + (r >> 5)) >> (r & 31)) & 1u) v += o.ytile[r];
     }
-    if (MODE == OUT_Y_ACCUM) v += to_acc(o.y[r]);
-    if (MODE == OUT_Y_PEERS) {
+    if (is_accum(MODE)) v += to_acc(o.y[r]);
+    if (is_peers(MODE)) {
         if constexpr (sizeof(V) == 8) {
             if (o.multicast()) {
                 multicast_store64(reinterpret_cast<double *>(o.multicast()) + o.row_offset + r, v);
@@ -489,7 +492,7 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
 
     // ---- coalesced epilogue: one row per thread per pass ----
     if (headOpen && nEmit > 0 && tid == 0) head[t] = ysum[0];  // the fix-up kernel finishes rows that span tiles
-    if constexpr (MODE == OUT_Y_PEERS && sizeof(V) == 2) {
+    if constexpr (is_peers(MODE) && sizeof(V) == 2) {
         if (out.multicast()) {  // warp-uniform loop: the lanes of a warp pair up their rows
             for (int qb = headOpen ? 1 : 0; qb < nEmit; qb += THREADS) {
                 const int q = qb + tid;
@@ -505,7 +508,7 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
             return;
         }
     }
-    if constexpr (MODE == OUT_Y_PEERS) {
+    if constexpr (is_peers(MODE)) {
         // plain peer stores: stage the tile's finished rows in the value type, then send 16-byte vectors.  FP64 rows
         // are staged in place; FP16 rows go to the padding tail of the product buffer (T/2 halves), so a tile that
         // closes more rows than that keeps the one-row-per-thread path below.
@@ -550,7 +553,7 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
                     if (HAS_TILE) {
                         if ((__ldg(out.hotmask + (r[k] >> 5)) >> (r[k] & 31)) & 1u) add[k] = out.ytile[r[k]];
                     }
-                    if (MODE == OUT_Y_ACCUM) add[k] += to_acc(out.y[r[k]]);
+                    if (is_accum(MODE)) add[k] += to_acc(out.y[r[k]]);
                 }
             }
         }
@@ -560,7 +563,7 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
             const A v = ysum[qs + k * THREADS] + add[k];
             if (MODE == OUT_CARRIER) {
                 out.carrier_out[dst[k]] = v;
-            } else if (MODE == OUT_Y_PEERS) {
+            } else if (is_peers(MODE)) {
                 if constexpr (sizeof(V) == 8) {
                     if (out.multicast()) {
                         multicast_store64(reinterpret_cast<double *>(out.multicast()) + out.row_offset + r[k], v);
@@ -720,7 +723,7 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     const bool hasTile = mode != OUT_CARRIER && ytile != nullptr && hotmask != nullptr;
     RowOut<V> out;
     out.y = (V *)y;
-    out.carrier_out = mode == OUT_Y_PEERS ? (A *)mc_y : (A *)y;
+    out.carrier_out = is_peers(mode) ? (A *)mc_y : (A *)y;
     out.row_map = row_map;
     out.ytile = (const A *)ytile;
     out.hotmask = hotmask;
@@ -738,7 +741,7 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     const int fgrid = (fwork + 127) / 128;
     cudaError_t le = cudaSuccess;
     // hot-column prefix of x in shared memory (persistent kernel): only where the plan says so and x is 16-byte aligned
-    const int hot = (P.hot_cols > 0 && ((uintptr_t)x & 15u) == 0 && mode != OUT_Y_ACCUM) ? P.hot_cols : 0;
+    const int hot = (P.hot_cols > 0 && ((uintptr_t)x & 15u) == 0 && !is_accum(mode)) ? P.hot_cols : 0;
 #define MX_LAUNCH(HT, MD)                                                                                           \
     do {                                                                                                            \
         if (hot > 0) {                                                                                              \
@@ -764,6 +767,8 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
     } while (0)
     if (mode == OUT_CARRIER)
         MX_LAUNCH(false, OUT_CARRIER);
+    else if (mode == OUT_Y_PEERS_ACCUM)
+        MX_LAUNCH(false, OUT_Y_PEERS_ACCUM);
     else if (mode == OUT_Y_PEERS && hasTile)
         MX_LAUNCH(true, OUT_Y_PEERS);
     else if (mode == OUT_Y_PEERS)
@@ -894,6 +899,16 @@ cudaError_t resid_spmv_peers(int dtype, const ResidPlan &P, const void *x, void 
                                     row_offset, mc_y);
     return resid_spmv_t<__half>(P, x, peers[0], ytile, hotmask, OUT_Y_PEERS, nullptr, s, chained, peers, n_peers,
                                 row_offset, mc_y);
+}
+
+cudaError_t resid_spmv_peers_accum(int dtype, const ResidPlan &P, const void *x, void *y_own, void *const *peers,
+                                   int n_peers, long long row_offset, cudaStream_t s, bool chained) {
+    if (n_peers < 1 || n_peers > MAX_PEERS) return cudaErrorInvalidValue;
+    if (dtype == MX_FP64)
+        return resid_spmv_t<double>(P, x, y_own, nullptr, nullptr, OUT_Y_PEERS_ACCUM, nullptr, s, chained, peers,
+                                    n_peers, row_offset, nullptr);
+    return resid_spmv_t<__half>(P, x, y_own, nullptr, nullptr, OUT_Y_PEERS_ACCUM, nullptr, s, chained, peers, n_peers,
+                                row_offset, nullptr);
 }
 
 cudaError_t resid_spmv_to_carrier(int dtype, const ResidPlan &P, const void *x, void *carrier, const int *row_map,

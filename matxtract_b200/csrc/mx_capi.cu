@@ -36,6 +36,7 @@ struct mx_handle_s {
     float tuning_ms = 0;            // host time the plan-time tuners took in the last mx_partition / mx_load_partition
     // column-slab execution of the plain CSR product (tau = (0,0)) when x is far larger than L2
     int slab_mode = -1;             // -1 = automatic, 0 = off, k >= 2 = k slabs
+    long long row_offset = 0;       // global index of the uploaded slab's first row (mx_set_row_offset)
     ColSlabs slabs;
     bool use_slabs = false;
     float slab_ms_plain = 0, slab_ms_slabbed = 0;
@@ -296,7 +297,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
                         bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0,
                         void *mc_y = nullptr) {
     if (peers && h->use_slabs && !h->stats.active) {
-        // column-slab passes accumulate into this GPU's own rows of its own y; the finished rows are then pushed
+        // far passes accumulate into this GPU's own rows of its own y; the band pass, last, sends the finished rows
         int self = -1;
         for (int g = 0; g < n_peers && self < 0; ++g) {
             cudaPointerAttributes at{};
@@ -308,9 +309,9 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         if (self < 0) return h->fail(MX_ERR_INVALID, "mx_spmv_peers: none of the buffers lives on this handle's GPU");
         const size_t vb = val_bytes(h->dtype);
         void *y_own = static_cast<char *>(peers[self]) + (size_t)row_offset * vb;
-        HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, h->stream));
-        int pst = mx_peer_push(h->dtype, peers, n_peers, self, row_offset, h->n_rows, h->peer_table, h->stream);
-        return pst == MX_OK ? MX_OK : h->fail(pst, "mx_spmv_peers: peer push failed");
+        HCK(col_slabs_spmv_peers(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, peers, n_peers, row_offset,
+                                 h->stream));
+        return MX_OK;
     }
     if (peers) {  // final rows go to every GPU's y
         const void *x = x_dev;
@@ -338,7 +339,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
                            /*chained=*/do_tile && h->dd_exec == MX_DD_CSR));
     } else if (do_resid) {
         if (h->use_slabs)
-            HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_dev, val_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
+            HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_dev, h->stream));
         else
             HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
     }
@@ -431,7 +432,7 @@ static int tune_col_slabs(mx_handle_t h) {
     A.row_ptr = h->row_ptr, A.col_ind = h->col_ind, A.val = h->val;
     if (h->slab_mode > 0) {  // forced
         int status = MX_OK;
-        HCK(col_slabs_build(h->dtype, A, h->slab_mode, h->slabs, &status, h->stream));
+        HCK(col_slabs_build(h->dtype, A, h->slab_mode, h->row_offset, h->slabs, &status, h->stream));
         h->use_slabs = status == MX_OK;  // rows not sorted by column: the plain kernel stays
         return MX_OK;
     }
@@ -463,7 +464,7 @@ static int tune_col_slabs(mx_handle_t h) {
         last = count;
         ColSlabs trial;
         int status = MX_OK;
-        HCK(col_slabs_build(h->dtype, A, count, trial, &status, h->stream));
+        HCK(col_slabs_build(h->dtype, A, count, h->row_offset, trial, &status, h->stream));
         if (status != MX_OK) return MX_OK;  // rows not sorted by column
         ColSlabs keep = h->slabs;
         h->slabs = trial;
@@ -978,11 +979,7 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
 int mx_spmv_launches(mx_handle_t h) {
     if (!h || !h->planned) return 0;
     int n = resid_launches(h->resid);
-    if (h->use_slabs) {
-        n = 0;
-        for (int k = 0; k < h->slabs.count; ++k)
-            if (h->slabs.plans[k].nnz > 0) n += resid_launches(h->slabs.plans[k]);
-    }
+    if (h->use_slabs) n = col_slabs_launches(h->slabs);
     if (h->stats.active)
         n += (h->use_orig_cols ? 0 : 1) + (h->dd_exec == MX_DD_TILE ? tile_launches(h->tile)
                                          : h->dd_exec == MX_DD_SE ? se_launches(h->se)
@@ -1036,6 +1033,12 @@ int mx_set_column_slabs(mx_handle_t h, int count) {
         col_slabs_free(h->slabs, h->stream);
         return tune_col_slabs(h);
     }
+    return MX_OK;
+}
+
+int mx_set_row_offset(mx_handle_t h, long long first_global_row) {
+    if (!h || first_global_row < 0) return MX_ERR_INVALID;
+    h->row_offset = first_global_row;
     return MX_OK;
 }
 

@@ -66,11 +66,15 @@ struct ResidPlan {
     void *head = nullptr;      // [num_tiles] accumulate-type partial of a first row that began in an earlier tile
 };
 
-// Column-slab execution of one CSR matrix (col_slabs.cu): the matrix cut into vertical slabs of `width` columns, each
-// stored as a CSR of its own over its non-empty rows and multiplied in a pass of its own that adds into y, so that the
-// x range a pass gathers from stays resident in L2.  Owned.
+// Column-slab execution of one CSR matrix (col_slabs.cu): the band around the diagonal as one CSR over all rows, the
+// far entries cut into vertical slabs of `width` columns, each a CSR of its own over its non-empty rows and multiplied
+// in a pass of its own that adds into y, so that the x range a pass gathers from stays resident in L2.  Owned.
 struct ColSlabs {
-    int count = 0, width = 0;
+    int count = 0, width = 0, halo = 0;
+    long long row_offset = 0;    // global index of the matrix's first row (a row slab of a larger square matrix)
+    ResidPlan near;              // the band; its arrays:
+    int *near_row_ptr = nullptr, *near_col = nullptr;
+    void *near_val = nullptr;
     ResidPlan *plans = nullptr;  // [count] host array; every plan owns its row tables, the struct owns col/val
     int **col = nullptr;         // [count] host array of device pointers
     void **val = nullptr;        // [count]
@@ -169,14 +173,24 @@ cudaError_t resid_spmv_peers(int dtype, const ResidPlan &plan, const void *x, vo
                              long long row_offset, const void *ytile, const uint32_t *hotmask, cudaStream_t s,
                              bool chained = false, void *mc_y = nullptr);
 int resid_launches(const ResidPlan &plan);
-// Cuts A (rows with ascending column ids) into `count` column slabs; *status = MX_ERR_INVALID when a row is not sorted.
-cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, ColSlabs &out, int *status, cudaStream_t s);
-void col_slabs_free(ColSlabs &S, cudaStream_t s);
-// y = A x (value type): y is cleared, then every slab adds its part.  2 launches per slab.
-cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
 // largest hot-column prefix (columns, rounded down to 16 bytes of values) the persistent CSR kernel can hold in shared
 // memory for this value type; 0 when `d_cols` is too small to be worth a persistent launch
 int resid_hot_cols_budget(int dtype, int d_cols);
+// Splits A (rows with ascending column ids) into its band and `count` column slabs of far entries; row_offset = global
+// index of A's first row; *status = MX_ERR_INVALID when a row is not sorted.
+cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, long long row_offset, ColSlabs &out, int *status,
+                            cudaStream_t s);
+void col_slabs_free(ColSlabs &S, cudaStream_t s);
+int col_slabs_launches(const ColSlabs &S);
+// y = A x (value type): the band pass writes every row, every far slab adds its part.
+cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, cudaStream_t s);
+// one GPU's share of a row-partitioned product: far passes accumulate in y_own, the band pass comes last and stores
+// the finished rows into every GPU's buffer
+cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *y_own, size_t y_bytes,
+                                 void *const *peers, int n_peers, long long row_offset, cudaStream_t s);
+// y_peer[g][row_offset + r] = y_own[r] + row r of the plan's matrix, for every g (y_own = this GPU's rows so far)
+cudaError_t resid_spmv_peers_accum(int dtype, const ResidPlan &plan, const void *x, void *y_own, void *const *peers,
+                                   int n_peers, long long row_offset, cudaStream_t s, bool chained);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
 void tile_plan_free(TilePlan &plan, cudaStream_t s);

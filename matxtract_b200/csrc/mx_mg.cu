@@ -274,6 +274,7 @@ int mx_mg_upload_csr(mx_mg_t mg, int n_rows, int n_cols, int nnz, const int *row
         int st = mx_upload_csr(mg->h[g], r1 - r0, n_cols, hi - lo, rp.data(), col_ind ? col_ind + lo : nullptr,
                                val ? static_cast<const char *>(val) + (size_t)lo * vb : nullptr);
         if (st != MX_OK) return mg->fail(st, mx_last_error_string(mg->h[g]));
+        mx_set_row_offset(mg->h[g], r0);
         MGCK(cudaSetDevice(mg->dev[g]));
         MGCK(cudaMalloc(&mg->x[g], vb * (size_t)std::max(n_cols, 1)));
         for (int k = 0; k < 2; ++k) {

@@ -142,6 +142,7 @@ class DistributedSpMV:
             self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
             self.handle = MatXtract(dtype, device=self.device.index)
             self.handle.upload_csr(self.rows, n_cols, rp, ci, v)
+            self.handle.set_row_offset(r0)
             if dd_executor is not None:  # fix the executor of the core-dense block instead of timing the three
                 self.handle.set_dd_executor(dd_executor)
             if world > 1 and ranking == "global" and tuple(float(t) for t in tau) != (0.0, 0.0):
