@@ -309,9 +309,15 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         if (self < 0) return h->fail(MX_ERR_INVALID, "mx_spmv_peers: none of the buffers lives on this handle's GPU");
         const size_t vb = val_bytes(h->dtype);
         void *y_own = static_cast<char *>(peers[self]) + (size_t)row_offset * vb;
-        HCK(col_slabs_spmv_peers(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, peers, n_peers, row_offset,
-                                 h->stream));
-        return MX_OK;
+        if (h->slabs.has_band) {
+            HCK(col_slabs_spmv_peers(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, peers, n_peers,
+                                     row_offset, h->stream));
+            return MX_OK;
+        }
+        // no band (the slab spans all columns' rows): accumulate locally, then push the finished rows
+        HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, h->stream));
+        int pst = mx_peer_push(h->dtype, peers, n_peers, self, row_offset, h->n_rows, h->peer_table, h->stream);
+        return pst == MX_OK ? MX_OK : h->fail(pst, "mx_spmv_peers: peer push failed");
     }
     if (peers) {  // final rows go to every GPU's y
         const void *x = x_dev;
@@ -339,7 +345,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
                            /*chained=*/do_tile && h->dd_exec == MX_DD_CSR));
     } else if (do_resid) {
         if (h->use_slabs)
-            HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_dev, h->stream));
+            HCK(col_slabs_spmv(h->dtype, h->slabs, x_dev, y_dev, val_bytes(h->dtype) * (size_t)h->n_rows, h->stream));
         else
             HCK(resid_spmv(h->dtype, h->resid, x_dev, y_dev, nullptr, nullptr, false, h->stream));
     }

@@ -72,6 +72,7 @@ struct ResidPlan {
 struct ColSlabs {
     int count = 0, width = 0, halo = 0;
     long long row_offset = 0;    // global index of the matrix's first row (a row slab of a larger square matrix)
+    bool has_band = false;       // row slabs only: the entries near the diagonal as a pass of their own
     ResidPlan near;              // the band; its arrays:
     int *near_row_ptr = nullptr, *near_col = nullptr;
     void *near_val = nullptr;
@@ -182,8 +183,8 @@ cudaError_t col_slabs_build(int dtype, const CsrDev &A, int count, long long row
                             cudaStream_t s);
 void col_slabs_free(ColSlabs &S, cudaStream_t s);
 int col_slabs_launches(const ColSlabs &S);
-// y = A x (value type): the band pass writes every row, every far slab adds its part.
-cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, cudaStream_t s);
+// y = A x (value type): the band pass writes every row (without a band y is cleared), every slab adds its part.
+cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
 // one GPU's share of a row-partitioned product: far passes accumulate in y_own, the band pass comes last and stores
 // the finished rows into every GPU's buffer
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *y_own, size_t y_bytes,

@@ -505,3 +505,45 @@ def test_slabs_extracted_with_global_rankings_reproduce_the_whole_partition(name
     check_y(dtype, np.concatenate(y), rp, ci, val, x)
     for h in hs + [whole]:
         h.close()
+
+
+def test_column_slabs_of_a_row_slab_with_its_band():
+    """One GPU's share of a row-partitioned matrix (rows [r0, r1) x all columns): the entries near the diagonal form a
+    band pass of their own, the far entries go through slab passes; through mx_spmv the band runs first, through
+    mx_spmv_peers (here with this GPU's buffer as the only peer) it runs last and writes the finished rows."""
+    import torch
+
+    n = 400_000
+    m = synth.generate("c5", n=n)
+    rp, ci, val, x = m["row_ptr"], m["col_ind"], m["val"], m["x"]
+    want = oracle.exact_spmv(rp, ci, val, x)
+    scale = oracle.abs_rowsum_max(FP64, rp, ci, val, x)
+    from matxtract_b200.distributed import slab
+
+    for r0, r1 in ((0, 150_001), (150_001, 333_333), (333_333, n)):
+        h = mx.MatXtract(FP64)
+        h.upload_csr(r1 - r0, n, *slab(rp, ci, val, r0, r1))
+        h.set_row_offset(r0)
+        h.partition(0.0, 0.0)
+        y_plain = h.spmv_host(x)
+        h.set_column_slabs(5)
+        assert h.column_slabs[0] == 5
+        y_slab = h.spmv_host(x)
+        assert np.abs(y_slab - want[r0:r1]).max() / scale <= TOL[FP64]
+        assert np.abs(y_slab - y_plain).max() <= 1e-13 * max(1.0, np.abs(y_plain).max())
+        np.testing.assert_array_equal(_bits(y_slab), _bits(h.spmv_host(x)))
+        # the fused-exchange order (far passes, band last) into a full-length buffer
+        stream = torch.cuda.ExternalStream(h.stream)
+        with torch.cuda.stream(stream):
+            x_dev = torch.from_numpy(x).cuda()
+            y_full = torch.full((n,), float("nan"), dtype=torch.float64, device="cuda")
+        stream.synchronize()
+        for _ in range(2):
+            h.spmv_peers(x_dev, [y_full.data_ptr()], r0)
+        h.sync()
+        got = y_full.cpu().numpy()
+        assert np.isnan(got[:r0]).all() and np.isnan(got[r1:]).all()  # only this slab's rows are written
+        assert np.abs(got[r0:r1] - want[r0:r1]).max() / scale <= TOL[FP64]
+        assert h.device_error() == 0
+        del x_dev, y_full
+        h.close()
