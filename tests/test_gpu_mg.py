@@ -36,6 +36,12 @@ def test_single_process_multi_gpu_product(name, n, tau):
         np.testing.assert_array_equal(g.bounds, mx.mg_partition_rows(rp, world))
         stats = g.partition(*tau)
         assert len(stats) == world and all(s.active == (1 if tau != (0.0, 0.0) else 0) for s in stats)
+        if world > 1 and tau != (0.0, 0.0):
+            # the rankings are those of the whole matrix: every slab has the same hot columns, and the slabs' hot
+            # rows add up to the whole matrix's (a slab that owns none still extracts one row)
+            whole = oracle.partition(dtype, n, n, rp, ci, val, *tau)["stats"]
+            assert {s.dCols for s in stats} == {whole["dCols"]}
+            assert whole["dRows"] <= sum(s.dRows for s in stats) <= whole["dRows"] + world
         y = g.spmv(x)
         assert oracle.y_error(dtype, y, y_ref, rp, ci, val, x) <= tol
         y2 = g.spmv(x)  # the second product lands in the other buffer
