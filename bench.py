@@ -793,6 +793,12 @@ def main():
                     help="hot-column prefix of x in shared memory (permuted numbering only)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU baseline leg (profiling runs)")
     args = ap.parse_args()
+    # torchrun pins every rank to one OpenMP thread; the input generator is host code that scales with threads, so give
+    # every rank its share of the cores (set before anything loads the OpenMP runtime)
+    world = max(1, int(os.environ.get("WORLD_SIZE", "1")))
+    if world > 1 or "OMP_NUM_THREADS" not in os.environ:
+        share = 1 if args.impl == "reference" else world  # the reference arm works on rank 0 only
+        os.environ["OMP_NUM_THREADS"] = str(max(1, cpu_threads() // share))
     if args.impl == "reference":
         run_reference(args)
     else:
