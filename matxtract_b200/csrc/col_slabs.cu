@@ -7,13 +7,17 @@
 //   * the BAND: the entries of every row whose column lies within COL_SLAB_HALO of the row's own index.  Their
 //     gathers walk x almost sequentially whatever its size, so the band is one ordinary CSR pass over all rows;
 //   * the FAR entries, cut into vertical slabs of `width` columns, each stored as its own CSR over its non-empty
-//     rows.  One pass per slab streams that slab's entries and gathers from an x range that stays in L2; the price
-//     is that the rows a pass touches are read and written once per pass.
-// All passes are the ordinary CSR kernel (resid_kernel), the far ones in its accumulate mode, so the arithmetic stays
-// free of atomics and bit-reproducible.  A whole (square) matrix has no band: its near-diagonal entries stay in the
-// slabs, y is cleared and every pass adds (one pass over y fewer).  One GPU's share of a row-partitioned matrix has
-// one: its far passes accumulate locally and the band pass runs LAST, storing the finished rows into every GPU's y
-// from its epilogue, so that the exchange overlaps the pass that holds about half of the work.
+//     rows.  One pass per slab streams that slab's entries and gathers from an x range that stays in L2.
+// A pass is the ordinary CSR kernel (resid_kernel) over the slab's NON-EMPTY rows as if they were a dense row space:
+// it writes one partial sum per such row into a buffer of its own, sequentially, and reads nothing but the slab and
+// x.  (Adding into y instead made every pass read and write the whole of y, a sector at a time, through a row-index
+// table: on the 1e9-non-zero shape 8 GB of the product's 28 GB of DRAM traffic.)  A last kernel (k_combine) walks the
+// rows once: a presence bit per (row, slab) and one base count per (32 rows, slab) locate every row's partial sums,
+// which it adds in slab order - the same order of additions as accumulating pass by pass, without atomics and
+// bit-reproducible.  A whole (square) matrix has no band: its near-diagonal entries stay in the slabs.  One GPU's
+// share of a row-partitioned matrix has one: the combined far sums land in its own rows and the band pass runs LAST,
+// adding them and storing the finished rows into every GPU's y from its epilogue, so that the exchange overlaps
+// the pass that holds about half of the work.
 // The reference has no counterpart: it runs one CSR kernel over the whole matrix (src/spmv_kernel/cdSpMV.cu:395-491).
 #include <algorithm>
 
@@ -131,7 +135,7 @@ template <typename V>
 __global__ void k_far_copy(const int *__restrict__ col, const V *__restrict__ val, const int *__restrict__ lo1,
                            const int *__restrict__ len1, const int *__restrict__ lo2, const int *__restrict__ len2,
                            const int *__restrict__ pos, const int *__restrict__ off, int n, int m_rows, int nnz_slab,
-                           int *__restrict__ c_ptr, int *__restrict__ nz_row, int *__restrict__ ocol,
+                           int *__restrict__ c_ptr, int *__restrict__ ocol,
                            V *__restrict__ oval) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31;
     int a1 = 0, l1 = 0, a2 = 0, l2 = 0, o = 0;
@@ -140,12 +144,52 @@ __global__ void k_far_copy(const int *__restrict__ col, const V *__restrict__ va
         if (l1 + l2 > 0) {
             const int k = pos[r];
             c_ptr[k] = o;
-            nz_row[k] = r;
         }
     }
     if (r == 0) c_ptr[m_rows] = nnz_slab;
     copy_ranges<V>(col, val, a1, l1, o, lane, ocol, oval);
     copy_ranges<V>(col, val, a2, l2, o + l1, lane, ocol, oval);
+}
+
+// slab k of the presence tables: flag[r] = the row has entries in the slab, pos = exclusive scan of flag
+__global__ void k_presence(const int *__restrict__ flag, const int *__restrict__ pos, int n, int k, int count,
+                           unsigned char *__restrict__ present, int *__restrict__ group_base) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    if (flag[r]) present[(size_t)(k >> 3) * n + r] |= (unsigned char)(1u << (k & 7));  // one thread per row: no race
+    if ((r & 31) == 0) group_base[(size_t)(r >> 5) * count + k] = pos[r];
+}
+
+// y[r] = sum over the slabs, in slab order, of the partial sum of row r (where the row has entries in the slab).
+// One lane per row: a ballot over the row's presence bit gives the lane's position among the warp's 32 rows, the
+// group's base count the position of the warp's first row, so consecutive present rows read consecutive partial sums.
+// (Column slabs exist for FP64 only: the passes and this kernel add in the value type.)
+__global__ void __launch_bounds__(256) k_combine(const double *const *__restrict__ part,
+                                                 const unsigned char *__restrict__ present,
+                                                 const int *__restrict__ group_base, int count, int n,
+                                                 double *__restrict__ y) {
+    const int r = blockIdx.x * 256 + threadIdx.x, lane = threadIdx.x & 31;
+    const bool live = r < n;
+    const unsigned below = (1u << lane) - 1u;
+    double acc = 0.0;
+    for (int k0 = 0; k0 < count; k0 += 8) {
+        const unsigned m = live ? (unsigned)__ldg(present + (size_t)(k0 >> 3) * n + r) : 0u;
+        int base = 0;
+        if (lane < 8 && k0 + lane < count && (r - lane) < n) base = __ldg(group_base + (size_t)(r >> 5) * count + k0 + lane);
+        double v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool bit = (m >> j) & 1u;
+            const unsigned b = __ballot_sync(0xffffffffu, bit);
+            const int bj = __shfl_sync(0xffffffffu, base, j);
+            v[j] = 0.0;
+            if (bit) v[j] = __ldg(part[k0 + j] + bj + __popc(b & below));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if ((m >> j) & 1u) acc += v[j];  // a row's absent slabs add nothing (not even +0)
+    }
+    if (live) y[r] = acc;
 }
 
 template <typename V>
@@ -183,9 +227,16 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
     out.width = width;
     out.halo = COL_SLAB_HALO;
     out.row_offset = row_offset;
+    out.n_rows = n;
     out.plans = new ResidPlan[count];
     out.col = new int *[count]();
     out.val = new void *[count]();
+    out.part = new void *[count]();
+    const size_t planes = ((size_t)count + 7) / 8, groups = ((size_t)n + 31) / 32;
+    CS_TRY(cudaMallocAsync(&out.present, std::max<size_t>(planes * (size_t)n, 1), s));
+    CS_TRY(cudaMemsetAsync(out.present, 0, std::max<size_t>(planes * (size_t)n, 1), s));
+    CS_TRY(cudaMallocAsync(&out.group_base, std::max<size_t>(groups * count, 1) * sizeof(int), s));
+    CS_TRY(cudaMallocAsync(&out.part_table, (size_t)count * sizeof(void *), s));
     // ---- the band: a CSR over all rows.  Only a row slab of a larger matrix (one GPU's share) has one: its band
     //      pass is what sends the finished rows to the other GPUs.  A whole matrix keeps its near-diagonal entries in
     //      the slabs (one pass over y fewer: measured 6.40 against 6.56 ms on the 1e9-nnz shape). ----
@@ -223,6 +274,7 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
                                               len, flag);
         CS_TRY(exclusive_sum(tmp, flag, pos, (int)n1, s));
         CS_TRY(exclusive_sum(tmp, len, off, (int)n1, s));
+        if (n > 0) k_presence<<<nblk(n), 256, 0, s>>>(flag, pos, n, k, count, out.present, out.group_base);
         int m_rows = 0, nnz_slab = 0;
         CS_TRY(cudaMemcpyAsync(&m_rows, pos + n, sizeof(int), cudaMemcpyDeviceToHost, s));
         CS_TRY(cudaMemcpyAsync(&nnz_slab, off + n, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -234,11 +286,11 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         P.m_rows = m_rows;
         P.n_empty = 0;  // rows without entries in this slab are not touched by its pass
         CS_TRY(cudaMallocAsync(&P.c_ptr_own, ((size_t)m_rows + 1) * sizeof(int), s));
-        CS_TRY(cudaMallocAsync(&P.nz_row, ((size_t)m_rows + 1) * sizeof(int), s));
+        CS_TRY(cudaMallocAsync(&out.part[k], (size_t)std::max(m_rows, 1) * sizeof(V), s));
         CS_TRY(cudaMallocAsync(&out.col[k], (size_t)std::max(nnz_slab, 1) * sizeof(int), s));
         CS_TRY(cudaMallocAsync(&out.val[k], (size_t)std::max(nnz_slab, 1) * sizeof(V), s));
         k_far_copy<V><<<nblk(std::max(n, 1)), 256, 0, s>>>(A.col_ind, (const V *)A.val, lo1, len1, lo2, len2, pos, off, n,
-                                                           m_rows, nnz_slab, P.c_ptr_own, P.nz_row, out.col[k],
+                                                           m_rows, nnz_slab, P.c_ptr_own, out.col[k],
                                                            (V *)out.val[k]);
         CS_TRY(cudaGetLastError());
         P.c_ptr = P.c_ptr_own;
@@ -247,6 +299,8 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         P.val = out.val[k];
         CS_TRY(resid_plan_finish(dtype, P, s));
     }
+    CS_TRY(cudaMemcpyAsync(out.part_table, out.part, (size_t)count * sizeof(void *), cudaMemcpyHostToDevice, s));
+    CS_TRY(cudaStreamSynchronize(s));
     return cudaSuccess;
 }
 
@@ -266,57 +320,76 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s) {
         if (S.plans) resid_plan_free(S.plans[k], s);
         if (S.col && S.col[k]) cudaFreeAsync(S.col[k], s);
         if (S.val && S.val[k]) cudaFreeAsync(S.val[k], s);
+        if (S.part && S.part[k]) cudaFreeAsync(S.part[k], s);
     }
+    for (void *p : {(void *)S.present, (void *)S.group_base, (void *)S.part_table})
+        if (p) cudaFreeAsync(p, s);
     resid_plan_free(S.near, s);
     for (void *p : {(void *)S.near_row_ptr, (void *)S.near_col, S.near_val})
         if (p) cudaFreeAsync(p, s);
     delete[] S.plans;
     delete[] S.col;
     delete[] S.val;
+    delete[] S.part;
     S = ColSlabs();
 }
 
 int col_slabs_launches(const ColSlabs &S) {
-    int n = S.has_band ? resid_launches(S.near) : 0;
+    int n = (S.has_band ? resid_launches(S.near) : 0) + 1;  // + the combining kernel
     for (int k = 0; k < S.count; ++k)
         if (S.plans[k].nnz > 0) n += resid_launches(S.plans[k]);
     return n;
 }
 
-// y = A x on one GPU: the band pass writes every row, the far passes add to it (each chained behind its predecessor:
-// its prologue overlaps the previous pass's tail).
-cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s) {
-    cudaError_t e;
-    bool first = true;
-    if (S.has_band) {
-        e = resid_spmv(dtype, S.near, x, y, nullptr, nullptr, /*accumulate=*/false, s);
-        first = false;
-    } else {
-        e = cudaMemsetAsync(y, 0, y_bytes, s);
-    }
+namespace {
+
+// the slab passes: pass k writes the partial sums of slab k's non-empty rows to S.part[k] (its row space is the
+// compressed one: the plan has no row-index table); each pass is chained behind its predecessor
+cudaError_t far_passes(int dtype, const ColSlabs &S, const void *x, cudaStream_t s, bool &first) {
+    cudaError_t e = cudaSuccess;
     for (int k = 0; k < S.count && e == cudaSuccess; ++k)
         if (S.plans[k].nnz > 0) {
-            e = resid_spmv(dtype, S.plans[k], x, y, nullptr, nullptr, /*accumulate=*/true, s, /*chained=*/!first);
+            e = resid_spmv(dtype, S.plans[k], x, S.part[k], nullptr, nullptr, /*accumulate=*/false, s, /*chained=*/!first);
             first = false;
         }
     return e;
 }
 
-// The same product as one GPU's share of a row-partitioned matrix: the far passes accumulate this GPU's rows in
-// y_own (its rows inside its own full-length buffer, cleared first); the band pass comes LAST, adds what y_own holds
-// and stores every finished row into all GPUs' buffers from its epilogue, so the exchange overlaps that pass.
+cudaError_t combine(int dtype, const ColSlabs &S, void *y, cudaStream_t s) {
+    if (S.n_rows <= 0) return cudaSuccess;
+    const int grid = (S.n_rows + 255) / 256;
+    if (dtype != MX_FP64) return cudaErrorNotSupported;
+    k_combine<<<grid, 256, 0, s>>>((const double *const *)S.part_table, S.present, S.group_base, S.count, S.n_rows,
+                                   (double *)y);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// y = A x on one GPU: one pass per slab, then the rows' partial sums are added in slab order.  (A matrix with a band
+// - a row slab of a larger matrix multiplied without peers - adds the band last, in the CSR kernel's accumulate mode.)
+cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s) {
+    (void)y_bytes;
+    bool first = true;
+    cudaError_t e = far_passes(dtype, S, x, s, first);
+    if (e == cudaSuccess) e = combine(dtype, S, y, s);
+    if (e == cudaSuccess && S.has_band)
+        e = resid_spmv(dtype, S.near, x, y, nullptr, nullptr, /*accumulate=*/true, s, /*chained=*/true);
+    return e;
+}
+
+// The same product as one GPU's share of a row-partitioned matrix: the far passes' partial sums are combined into
+// y_own (this GPU's rows inside its own full-length buffer); the band pass comes LAST, adds what y_own holds and
+// stores every finished row into all GPUs' buffers from its epilogue, so the exchange overlaps that pass.
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *y_own, size_t y_bytes,
                                  void *const *peers, int n_peers, long long row_offset, cudaStream_t s) {
-    cudaError_t e = cudaMemsetAsync(y_own, 0, y_bytes, s);
+    (void)y_bytes;
+    if (!S.has_band) return cudaErrorNotSupported;  // without a band the caller pushes the finished rows itself
     bool first = true;
-    for (int k = 0; k < S.count && e == cudaSuccess; ++k)
-        if (S.plans[k].nnz > 0) {
-            e = resid_spmv(dtype, S.plans[k], x, y_own, nullptr, nullptr, /*accumulate=*/true, s, /*chained=*/!first);
-            first = false;
-        }
+    cudaError_t e = far_passes(dtype, S, x, s, first);
+    if (e == cudaSuccess) e = combine(dtype, S, y_own, s);
     if (e != cudaSuccess) return e;
-    if (S.has_band) return resid_spmv_peers_accum(dtype, S.near, x, y_own, peers, n_peers, row_offset, s, !first);
-    return cudaErrorNotSupported;  // without a band the caller pushes the finished rows itself
+    return resid_spmv_peers_accum(dtype, S.near, x, y_own, peers, n_peers, row_offset, s, /*chained=*/true);
 }
 
 }  // namespace mx

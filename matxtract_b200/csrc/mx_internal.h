@@ -68,7 +68,8 @@ struct ResidPlan {
 
 // Column-slab execution of one CSR matrix (col_slabs.cu): the band around the diagonal as one CSR over all rows, the
 // far entries cut into vertical slabs of `width` columns, each a CSR of its own over its non-empty rows and multiplied
-// in a pass of its own that adds into y, so that the x range a pass gathers from stays resident in L2.  Owned.
+// in a pass of its own, so that the x range a pass gathers from stays resident in L2.  A pass writes one partial sum
+// per non-empty row of its slab, densely; a last kernel adds every row's partial sums in slab order.  Owned.
 struct ColSlabs {
     int count = 0, width = 0, halo = 0;
     long long row_offset = 0;    // global index of the matrix's first row (a row slab of a larger square matrix)
@@ -79,6 +80,11 @@ struct ColSlabs {
     ResidPlan *plans = nullptr;  // [count] host array; every plan owns its row tables, the struct owns col/val
     int **col = nullptr;         // [count] host array of device pointers
     void **val = nullptr;        // [count]
+    void **part = nullptr;       // [count] host array: partial sums (value type) of slab k's non-empty rows, in row order
+    void **part_table = nullptr; // the same pointers on the device
+    unsigned char *present = nullptr;  // [(count+7)/8][n_rows]: bit k%8 of plane k/8 set when the row has entries in slab k
+    int *group_base = nullptr;   // [ceil(n_rows/32)][count]: non-empty rows of slab k before the group's first row
+    int n_rows = 0;
 };
 
 // Plain CSR on the device (non-owning view).
