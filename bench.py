@@ -421,6 +421,9 @@ def run_ours(args):
 
     x_host = torch.from_numpy(m["x"].view(np.int16 if dtype == mx.FP16 else np.float64)).view(tdt).pin_memory()
     y_host = torch.empty(n_local, dtype=tdt).pin_memory()  # what this rank's caller owns: its slab of y
+    # end-to-end legs alternate between two pairs of pinned host buffers (consecutive products of a caller)
+    x_host2 = (x_host.clone() if world == 1 else x_host[r0:r1].clone()).pin_memory()
+    y_host2 = torch.empty(n_local, dtype=tdt).pin_memory()
     with torch.cuda.stream(stream):
         x_dev = x_host.to(dev, non_blocking=True)
         y_full = torch.zeros(n_total, dtype=tdt, device=dev)
@@ -452,25 +455,26 @@ def run_ours(args):
         pad_in = torch.zeros(longest, dtype=tdt, device=dev)
         pad_out = torch.empty(world * longest, dtype=tdt, device=dev)
 
-    def enqueue_product():
+    def enqueue_product(x=None):
         """This rank's launches of one step (no barrier / collective)."""
+        x = x_dev if x is None else x
         if world == 1:
-            h.spmv(x_dev, y_full)
+            h.spmv(x, y_full)
         elif method[0] == "epilogue":
             buf, ptrs = peer_y.next()
-            h.spmv_peers(x_dev, ptrs, r0)
+            h.spmv_peers(x, ptrs, r0)
             last_y[0] = buf
         elif method[0] == "multicast":
             buf, ptrs = peer_y.next()
-            h.spmv_multicast(x_dev, ptrs, peer_y.multicast_ptr, r0)
+            h.spmv_multicast(x, ptrs, peer_y.multicast_ptr, r0)
             last_y[0] = buf
         elif method[0] == "push":
             buf, ptrs = peer_y.next()
-            h.spmv(x_dev, buf[r0:r1])
+            h.spmv(x, buf[r0:r1])
             h.peer_push(ptrs, rank, r0, n_local, push_table)
             last_y[0] = buf
         else:
-            h.spmv(x_dev, y_work)
+            h.spmv(x, y_work)
 
     def enqueue_exchange():
         if world == 1:
@@ -492,16 +496,37 @@ def run_ours(args):
         enqueue_product()
         enqueue_exchange()
 
+    e2e_k = [0]
+    peer_x = [None]
+
     def step_e2e():
-        if world == 1:  # the C-ABI call with host buffers: x in, product, y out, synchronise
-            h.spmv_host(x_host, y_host)
+        """One product from and to HOST memory.  1 GPU: the pipelined C-ABI call (x in, product, y out on three
+        streams; the timed region ends with mx_host_sync).  N GPUs: every rank copies in its own share of x (the rows
+        it owns of y), the shares are exchanged over NVLink (peer stores + one barrier), then product + y exchange,
+        then the rank's slab of y goes back to its host."""
+        e2e_k[0] ^= 1
+        xh, yh = (x_host, y_host) if e2e_k[0] else (x_host2, y_host2)
+        if world == 1:
+            h.spmv_host_async(xh, yh)
             return
+        if peer_x[0] is None:  # without symmetric memory: the whole x from this rank's host
+            with torch.cuda.stream(stream):
+                x_dev.copy_(x_host, non_blocking=True)
+            step_device()
+        else:
+            xbuf, xptrs = peer_x[0].next()
+            with torch.cuda.stream(stream):
+                xbuf[r0:r1].copy_(x_host2, non_blocking=True)  # this rank's share of x
+            h.peer_push(xptrs, rank, r0, n_local, push_table)
+            with torch.cuda.stream(stream):
+                peer_x[0].finish()
+            enqueue_product(xbuf)
+            enqueue_exchange()
         with torch.cuda.stream(stream):
-            x_dev.copy_(x_host, non_blocking=True)
-        step_device()
-        with torch.cuda.stream(stream):
-            y_host.copy_(last_y[0][r0:r1], non_blocking=True)
-        stream.synchronize()
+            yh.copy_(last_y[0][r0:r1], non_blocking=True)
+
+    def step_e2e_single_call():  # the synchronous C-ABI call: one product's latency with host buffers
+        h.spmv_host(x_host, y_host)
 
     def barrier():
         stream.synchronize()
@@ -517,12 +542,15 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(fn, steps, warmup, min_total_ms=200.0, max_repeats=20):
+    def timed(fn, steps, warmup, min_total_ms=200.0, max_repeats=20, finish=None):
         """ms per step: EXACTLY `steps` steps between two events on the handle's stream, barrier + synchronise on both
         sides, max over ranks; the region is repeated until the repeats cover min_total_ms (so that the clock sampler
-        sees the load) and the median repeat is returned."""
+        sees the load) and the median repeat is returned.  finish (optional) runs after the last step, before the
+        closing event: the pipelined host call ends its work on a copy stream, which finish waits for."""
         for _ in range(warmup):
             fn()
+        if finish:
+            finish()
         reps = []
         total = 0.0
         while True:
@@ -532,6 +560,8 @@ def run_ours(args):
             e0.record(stream)
             for _ in range(steps):
                 fn()
+            if finish:
+                finish()
             e1.record(stream)
             barrier()
             sampler.active.clear()
@@ -565,15 +595,31 @@ def run_ours(args):
         method[0] = min(trial, key=trial.get).split(",")[0]
     ms_step, repeats = timed(step_device, args.steps, max(3, args.warmup))
     value = 2.0 * nnz_total / (ms_step * 1e-3) / 1e9
-    ms_e2e, _ = timed(step_e2e, max(10, args.steps // 10), 3, min_total_ms=0.0)
+    if world > 1 and peer_y is not None:
+        try:
+            with torch.cuda.stream(stream):
+                peer_x[0] = PeerY(n_total, tdt, dev)
+        except Exception:
+            peer_x[0] = None
+    ms_e2e, _ = timed(step_e2e, max(10, args.steps // 10), 3, min_total_ms=0.0,
+                      finish=h.host_sync if world == 1 else None)
     e2e_value = 2.0 * nnz_total / (ms_e2e * 1e-3) / 1e9
+    ms_e2e_single = timed(step_e2e_single_call, 5, 2, min_total_ms=0.0)[0] if world == 1 else None
 
     # ---- parity of the product that was just timed (every N): sampled rows of the gathered y on rank 0 against the
     #      reference's serial SpMV, and all GPUs' copies of y compared with each other ----
     step_device()
     barrier()
     y_final = last_y[0]
+    # the host-buffer leg must have produced the same bits as the device-resident product (same x)
+    y_e2e = y_host if e2e_k[0] else y_host2
+    e2e_same = bool(torch.equal(y_e2e.view(torch.int16 if dtype == mx.FP16 else torch.int64),
+                                y_final[r0:r1].cpu().view(torch.int16 if dtype == mx.FP16 else torch.int64)))
     replicas_identical = None
+    if dist is not None:
+        t = torch.tensor([1.0 if e2e_same else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        e2e_same = bool(t.item() == 1.0)
     if dist is not None:
         ck = y_final.view(torch.int64 if dtype == mx.FP64 else torch.int16).to(torch.int64).sum().reshape(1)
         allck = [torch.zeros_like(ck) for _ in range(world)]
@@ -667,13 +713,14 @@ def run_ours(args):
 
     def shutdown():
         # torch tensors that lived on the handle's stream must go before the stream does
-        nonlocal x_dev, y_full, y_work, x_host, y_host, peer_y, push_table, y_final
+        nonlocal x_dev, y_full, y_work, x_host, y_host, x_host2, y_host2, peer_y, push_table, y_final
         stream.synchronize()
         last_y[0] = None
         peer_y = None
+        peer_x[0] = None
         push_table = None
         y_final = None
-        del x_dev, y_full, y_work, x_host, y_host  # pinned buffers record events on the stream when freed
+        del x_dev, y_full, y_work, x_host, y_host, x_host2, y_host2  # pinned buffers record events on the stream when freed
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
         h.close()
@@ -747,10 +794,15 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
                      "stream_gather_floor_ms": gather_floor_ms,
                      "floor_over_step": gather_floor_ms / (ms_step if world == 1 else halves["ms_total"])},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": n_total * vb,
-                "d2h_bytes_per_step": n_local * vb,
-                "path": "mx_spmv_host (C ABI, pinned host x in, host y out)" if world == 1 else
-                "per rank: pinned x -> device, product + exchange, this rank's slab of y -> pinned host"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": n_total * vb if (world == 1 or peer_x[0] is not None) else world * n_total * vb,
+                "d2h_bytes_per_step": n_total * vb,  # whole job: every rank its own share
+                "path": "mx_spmv_host_async x steps + mx_host_sync (C ABI; pinned host x in, product, host y out, the "
+                        "copies of consecutive products overlapping the kernels)" if world == 1 else
+                ("per rank: its share of x from pinned host memory, shares exchanged over NVLink (peer stores + "
+                 "barrier), product + y exchange, this rank's slab of y -> pinned host" if peer_x[0] is not None else
+                 "per rank: pinned x -> device, product + exchange, this rank's slab of y -> pinned host"),
+                "ms_per_step_single_synchronous_call": ms_e2e_single,
+                "same_bits_as_the_device_resident_product": e2e_same},
         "gpu_launches": (h.launches_per_spmv + (1 if method[0] == "push" else 0)) * args.steps * repeats,
         "clocks": sampler.summary(),
         "cpu_baseline": cpu,

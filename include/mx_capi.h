@@ -206,6 +206,16 @@ int mx_mg_spmv_timed(mx_mg_t mg, const void *x_host, int warm, int iters, float 
 
 /* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
+/* A sequence of products with HOST pointers, pipelined: the call enqueues "copy x in, multiply, copy y out" and
+ * returns; the copy in, the kernels and the copy out of consecutive calls run on three streams over two sets of
+ * device buffers, so that the transfers of one product overlap the kernels of its neighbours (PCIe carries both
+ * directions at once).  x_host and y_host should be page-locked (pageable memory works but does not overlap) and
+ * must stay valid, x unmodified and y unread, until mx_host_sync returns.  Any number of calls may precede one
+ * mx_host_sync; results are identical to mx_spmv_host.  Mirrors the reference's per-call cudaMemcpy in / out of
+ * every wrapper (src/spmv_kernel/cdSpMV.cu:405-420,483-486), which it issues synchronously around each product. */
+int mx_spmv_host_async(mx_handle_t h, const void *x_host, void *y_host);
+/* Waits for every product enqueued with mx_spmv_host_async (and for the handle's stream). */
+int mx_host_sync(mx_handle_t h);
 /* Timing loop on the device: `warm` untimed and `iters` timed repetitions (the reference uses 200 and
  * 4000, src/spmv_kernel/cdSpMV.cu:454-455).  ms_tile / ms_resid time each half alone, as the reference's
  * "MatXtract time = tcTime + cdTime" does (:1564); ms_total times the real back-to-back sequence. */

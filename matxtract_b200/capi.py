@@ -82,6 +82,8 @@ SYMBOLS = {
     "mx_download_partition": (_i, [_vp, C.POINTER(_PartitionArrays)]),
     "mx_spmv": (_i, [_vp, _vp, _vp]),
     "mx_spmv_host": (_i, [_vp, _vp, _vp]),
+    "mx_spmv_host_async": (_i, [_vp, _vp, _vp]),
+    "mx_host_sync": (_i, [_vp]),
     "mx_spmv_peers": (_i, [_vp, _vp, C.POINTER(_vp), _i, C.c_longlong]),
     "mx_spmv_multicast": (_i, [_vp, _vp, C.POINTER(_vp), _i, _vp, C.c_longlong]),
     "mx_peer_push": (_i, [_i, C.POINTER(_vp), _i, _i, C.c_longlong, C.c_longlong, _vp, _vp]),
@@ -309,6 +311,15 @@ class MatXtract:
             y = np.empty(self.n_rows, np_dtype(self.dtype))
         self._ck(lib().mx_spmv_host(self._h, _ptr(x), _ptr(y)))
         return y
+
+    def spmv_host_async(self, x, y):
+        """Enqueues y = A x with HOST buffers and returns; consecutive calls overlap their copies with each other's
+        kernels.  x and y (numpy arrays or torch CPU tensors of the handle's value type, page-locked for the overlap)
+        must stay alive and untouched until host_sync()."""
+        self._ck(lib().mx_spmv_host_async(self._h, _ptr(x), _ptr(y)))
+
+    def host_sync(self):
+        self._ck(lib().mx_host_sync(self._h))
 
     def spmv_timed(self, x_dev, y_dev, warm=20, iters=200):
         t, r, a = C.c_float(), C.c_float(), C.c_float()

@@ -56,6 +56,12 @@ struct mx_handle_s {
     void *x_perm = nullptr;  // [n_cols] x in partition order
     // staging for the host-pointer entry point
     void *x_stage = nullptr, *y_stage = nullptr;
+    // pipelined host-pointer products (mx_spmv_host_async): a second pair of staging buffers, one stream per copy
+    // direction, and per slot the events "x has arrived", "product done", "y has left"
+    void *x_stage2 = nullptr, *y_stage2 = nullptr;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+    unsigned long long async_calls = 0;
     int *dev_err = nullptr;
 
     int fail(int status, const std::string &msg) {
@@ -118,11 +124,14 @@ void drop_plan(mx_handle_t h) {
 
 void drop_matrix(mx_handle_t h) {
     drop_plan(h);
-    void *bufs[] = {h->row_ptr, h->col_ind, h->val, h->x_stage, h->y_stage};
+    if (h->copy_in) cudaStreamSynchronize(h->copy_in);  // copies of a pipelined product may still use the buffers
+    if (h->copy_out) cudaStreamSynchronize(h->copy_out);
+    void *bufs[] = {h->row_ptr, h->col_ind, h->val, h->x_stage, h->y_stage, h->x_stage2, h->y_stage2};
     for (void *b : bufs)
         if (b) cudaFreeAsync(b, h->stream);
     h->row_ptr = h->col_ind = nullptr;
-    h->val = h->x_stage = h->y_stage = nullptr;
+    h->val = h->x_stage = h->y_stage = h->x_stage2 = h->y_stage2 = nullptr;
+    h->async_calls = 0;
     h->has_matrix = false;
     h->n_rows = h->n_cols = h->nnz = 0;
 }
@@ -216,6 +225,11 @@ int mx_destroy(mx_handle_t h) {
     cudaStreamSynchronize(h->stream);
     cudaFree(h->dev_err);
     cudaFree(h->peer_table);
+    for (int i = 0; i < 2; ++i)
+        for (cudaEvent_t e : {h->ev_in[i], h->ev_done[i], h->ev_out[i]})
+            if (e) cudaEventDestroy(e);
+    if (h->copy_in) cudaStreamDestroy(h->copy_in);
+    if (h->copy_out) cudaStreamDestroy(h->copy_out);
     cudaStreamDestroy(h->stream);
     delete h;
     return MX_OK;
@@ -979,6 +993,61 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
     if (st != MX_OK) return st;
     HCK(cudaMemcpyAsync(y_host, h->y_stage, vb * (size_t)h->n_rows, cudaMemcpyDeviceToHost, h->stream));
     HCK(cudaStreamSynchronize(h->stream));
+    return MX_OK;
+}
+
+// Products with host buffers, pipelined: the copy of x in, the product and the copy of y out run on three streams
+// over two sets of staging buffers, so the transfers of one product overlap the kernels of its neighbours.
+int mx_spmv_host_async(mx_handle_t h, const void *x_host, void *y_host) {
+    if (!h || !x_host || !y_host) return MX_ERR_INVALID;
+    if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_host_async: call mx_partition first");
+    HCK(cudaSetDevice(h->device));
+    const size_t vb = val_bytes(h->dtype);
+    const size_t xb = vb * (size_t)(h->n_cols > 0 ? h->n_cols : 1), yb = vb * (size_t)(h->n_rows > 0 ? h->n_rows : 1);
+    if (!h->copy_in) {  // first use: the second buffer pair, the copy streams and the events
+        HCK(cudaStreamSynchronize(h->stream));
+        HCK(cudaMallocAsync(&h->x_stage2, xb, h->stream));
+        HCK(cudaMallocAsync(&h->y_stage2, yb, h->stream));
+        HCK(cudaStreamSynchronize(h->stream));
+        for (int i = 0; i < 2; ++i) {
+            HCK(cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+            HCK(cudaEventCreateWithFlags(&h->ev_done[i], cudaEventDisableTiming));
+            HCK(cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+        }
+        HCK(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+        HCK(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+    } else if (!h->x_stage2) {  // a new matrix was uploaded since
+        HCK(cudaMallocAsync(&h->x_stage2, xb, h->stream));
+        HCK(cudaMallocAsync(&h->y_stage2, yb, h->stream));
+    }
+    const int slot = (int)(h->async_calls & 1ull);
+    const bool reuse = h->async_calls >= 2;  // the slot's previous product must have left it
+    void *xs = slot ? h->x_stage2 : h->x_stage, *ys = slot ? h->y_stage2 : h->y_stage;
+    if (h->async_calls < 2) {  // the buffers were allocated (or last used) on the compute stream
+        HCK(cudaEventRecord(h->ev_done[slot], h->stream));
+        HCK(cudaStreamWaitEvent(h->copy_in, h->ev_done[slot], 0));
+    }
+    if (reuse) HCK(cudaStreamWaitEvent(h->copy_in, h->ev_done[slot], 0));  // its product has read x
+    HCK(cudaMemcpyAsync(xs, x_host, vb * (size_t)h->n_cols, cudaMemcpyHostToDevice, h->copy_in));
+    HCK(cudaEventRecord(h->ev_in[slot], h->copy_in));
+    HCK(cudaStreamWaitEvent(h->stream, h->ev_in[slot], 0));
+    if (reuse) HCK(cudaStreamWaitEvent(h->stream, h->ev_out[slot], 0));  // its y has left the buffer
+    int st = spmv_enqueue(h, xs, ys, true, true);
+    if (st != MX_OK) return st;
+    HCK(cudaEventRecord(h->ev_done[slot], h->stream));
+    HCK(cudaStreamWaitEvent(h->copy_out, h->ev_done[slot], 0));
+    HCK(cudaMemcpyAsync(y_host, ys, vb * (size_t)h->n_rows, cudaMemcpyDeviceToHost, h->copy_out));
+    HCK(cudaEventRecord(h->ev_out[slot], h->copy_out));
+    ++h->async_calls;
+    return MX_OK;
+}
+
+int mx_host_sync(mx_handle_t h) {
+    if (!h) return MX_ERR_INVALID;
+    HCK(cudaSetDevice(h->device));
+    if (h->copy_in) HCK(cudaStreamSynchronize(h->copy_in));
+    HCK(cudaStreamSynchronize(h->stream));
+    if (h->copy_out) HCK(cudaStreamSynchronize(h->copy_out));
     return MX_OK;
 }
 

@@ -511,8 +511,9 @@ def test_slabs_extracted_with_global_rankings_reproduce_the_whole_partition(name
 
 def test_column_slabs_of_a_row_slab_with_its_band():
     """One GPU's share of a row-partitioned matrix (rows [r0, r1) x all columns): the entries near the diagonal form a
-    band pass of their own, the far entries go through slab passes; through mx_spmv the band runs first, through
-    mx_spmv_peers (here with this GPU's buffer as the only peer) it runs last and writes the finished rows."""
+    band pass of their own, the far entries go through slab passes whose partial sums are combined first; the band
+    pass runs last and adds to them - through mx_spmv into y, through mx_spmv_peers (here with this GPU's buffer as
+    the only peer) into every GPU's buffer."""
     import torch
 
     n = 400_000
@@ -549,3 +550,40 @@ def test_column_slabs_of_a_row_slab_with_its_band():
         assert h.device_error() == 0
         del x_dev, y_full
         h.close()
+
+
+@pytest.mark.parametrize("dtype", [FP64, FP16])
+def test_pipelined_host_products_equal_the_synchronous_call(dtype):
+    """mx_spmv_host_async: five products with different x enqueued back to back over the two staging slots (pinned
+    buffers), one mx_host_sync; every y equals, bit for bit, what mx_spmv_host returns for the same x - before and
+    after a new matrix is uploaded into the same handle, with and without an active partition."""
+    import torch
+
+    tdt = torch.float64 if dtype == FP64 else torch.float16
+    h = mx.MatXtract(dtype)
+    for n, per_row, tau in ((30_000, 9, (0.0, 0.0)), (12_345, 14, (0.5, 0.3))):
+        rp, ci = random_csr(n, per_row, 21 + n)
+        val = values(dtype, len(ci), 22)
+        h.upload_csr(n, n, rp, ci, val)
+        h.partition(*tau)
+        xs = [values(dtype, n, 100 + i) for i in range(5)]
+        want = [h.spmv_host(x).copy() for x in xs]
+        check_y(dtype, want[0], rp, ci, val, xs[0])
+        as_t = lambda a: torch.from_numpy(a.view(np.int16) if dtype == FP16 else a).view(tdt)
+        x_pin = [as_t(x).pin_memory() for x in xs]
+        y_pin = [torch.full((n,), float("nan"), dtype=tdt).pin_memory() for _ in xs]
+        for rounds in range(2):
+            for xp, yp in zip(x_pin, y_pin):
+                h.spmv_host_async(xp, yp)
+            h.host_sync()
+            for yp, w in zip(y_pin, want):
+                got = yp.numpy() if dtype == FP64 else yp.view(torch.int16).numpy().view(np.float16)
+                np.testing.assert_array_equal(_bits(got), _bits(w))
+                yp.fill_(float("nan"))
+        # pageable memory is accepted too (no overlap, same result)
+        y_np = np.empty(n, mx.capi.np_dtype(dtype))
+        h.spmv_host_async(xs[1], y_np)
+        h.host_sync()
+        np.testing.assert_array_equal(_bits(y_np), _bits(want[1]))
+    assert h.device_error() == 0
+    h.close()
