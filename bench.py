@@ -615,6 +615,7 @@ def run_ours(args):
     y_e2e = y_host if e2e_k[0] else y_host2
     e2e_same = bool(torch.equal(y_e2e.view(torch.int16 if dtype == mx.FP16 else torch.int64),
                                 y_final[r0:r1].cpu().view(torch.int16 if dtype == mx.FP16 else torch.int64)))
+    del y_e2e  # a pinned buffer: no reference may outlive shutdown()
     replicas_identical = None
     if dist is not None:
         t = torch.tensor([1.0 if e2e_same else 0.0], device=dev, dtype=torch.float64)
@@ -721,6 +722,9 @@ def run_ours(args):
         push_table = None
         y_final = None
         del x_dev, y_full, y_work, x_host, y_host, x_host2, y_host2  # pinned buffers record events on the stream when freed
+        import gc
+
+        gc.collect()
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
         h.close()
