@@ -163,7 +163,9 @@ __global__ void k_presence(const int *__restrict__ flag, const int *__restrict__
 // y[r] = sum over the slabs, in slab order, of the partial sum of row r (where the row has entries in the slab).
 // One lane per row: a ballot over the row's presence bit gives the lane's position among the warp's 32 rows, the
 // group's base count the position of the warp's first row, so consecutive present rows read consecutive partial sums.
-// (Column slabs exist for FP64 only: the passes and this kernel add in the value type.)
+// (Measured and rejected on the 1e9-non-zero shape: four groups of 32 rows per warp with all 32 loads of a lane in
+// flight, 102 registers: +0.41 ms; a warp walking 8 consecutive groups with the next group's presence bits requested
+// ahead: +0.12 ms.  Column slabs exist for FP64 only: the passes and this kernel add in the value type.)
 __global__ void __launch_bounds__(256) k_combine(const double *const *__restrict__ part,
                                                  const unsigned char *__restrict__ present,
                                                  const int *__restrict__ group_base, int count, int n,
@@ -285,6 +287,7 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         P.nnz = nnz_slab;
         P.m_rows = m_rows;
         P.n_empty = 0;  // rows without entries in this slab are not touched by its pass
+        P.dense_row_ends = (long long)m_rows * 16 >= nnz_slab;  // 128 or more row ends per tile of 2048 non-zeros
         CS_TRY(cudaMallocAsync(&P.c_ptr_own, ((size_t)m_rows + 1) * sizeof(int), s));
         CS_TRY(cudaMallocAsync(&out.part[k], (size_t)std::max(m_rows, 1) * sizeof(V), s));
         CS_TRY(cudaMallocAsync(&out.col[k], (size_t)std::max(nnz_slab, 1) * sizeof(int), s));

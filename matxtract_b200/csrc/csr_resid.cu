@@ -294,14 +294,21 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cuda
 
 // Shared-memory working set of one tile (one per CTA in the one-tile-per-CTA kernel, one per thread group in the
 // persistent kernel).
-template <typename A, int T, int NW>
+template <typename A, int T, int NW, bool DENSE = false>
 struct __align__(16) TileSmem {
     static constexpr int PADW = 16 / (int)sizeof(A);
     A sp[T + (T / 16) * PADW];  // products, padded; reused for the sums of the rows that end in the tile
-    unsigned sFlag[T / 32];     // bit i set: a row ends after the tile's i-th non-zero
-    int sFirst[T / 32];         // lowest row (relative) that ends inside the 32-nnz word
+    // where the tile's rows end, in one of two encodings:
+    union {
+        struct {
+            unsigned sFlag[T / 32];  // bit i set: a row ends after the tile's i-th non-zero
+            int sFirst[T / 32];      // lowest row (relative) that ends inside the 32-nnz word
+        };
+        unsigned char sEnd[DENSE ? T : 16];  // DENSE: one byte per non-zero, 1 = a row ends after it
+    };
     A warpTail[NW];
     int warpOpen[NW];
+    int warpEnds[NW];  // DENSE: rows that end inside the warp's share of the tile
 };
 
 // barrier over the RESID_THREADS threads that work on one tile: the whole CTA, or one group of a persistent CTA
@@ -324,9 +331,14 @@ __device__ __forceinline__ V load_x(const V *__restrict__ x, const V *xs, int ho
 }
 
 // One tile (T consecutive non-zeros) of the product, by the RESID_THREADS threads tid = 0..RESID_THREADS-1.
-template <typename V, int IPT, bool HAS_TILE, int MODE, int GROUPS, bool HOTX>
+// DENSE selects how the row ends of a tile are marked.  false: one bit per non-zero in shared words plus the lowest row
+// per word, set with two shared-memory atomics per row end - cheapest when a tile closes few rows.  true: one byte per
+// non-zero set with plain stores, the row index of a thread's first end from a scan of the threads' end counts - no
+// atomics, which serialise on the words neighbouring rows share when a tile closes hundreds of rows (a column-slab
+// pass closes ~480 per tile: 3.4 % faster on the 1e9-non-zero shape; 1-3 % slower on the other benchmark shapes).
+template <typename V, int IPT, bool HAS_TILE, int MODE, int GROUPS, bool HOTX, bool DENSE = false>
 __device__ __forceinline__ void resid_tile(const int t, const int tid, const int grp, const int numTiles,
-                                           TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32> &sm,
+                                           TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32, DENSE> &sm,
                                            const V *xs, const int hotCols, const int *__restrict__ cPtr,
                                            const int *__restrict__ colInd, const V *__restrict__ val,
                                            const V *__restrict__ x, const RowOut<V> &out,
@@ -386,9 +398,13 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
     // ends are in [0, cnt): rows are non-empty, so they are distinct
     const int e0 = tid < nEmit ? __ldg(ce + 1 + tid) - base - 1 : -1;
     const int e1 = tid + THREADS < nEmit ? __ldg(ce + 1 + tid + THREADS) - base - 1 : -1;
-    for (int i = tid; i < T / 32; i += THREADS) {
-        sFlag[i] = 0u;
-        sFirst[i] = INT_MAX;
+    if constexpr (DENSE) {
+        for (int i = tid; i < T / 16; i += THREADS) reinterpret_cast<uint4 *>(sm.sEnd)[i] = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        for (int i = tid; i < T / 32; i += THREADS) {
+            sFlag[i] = 0u;
+            sFirst[i] = INT_MAX;
+        }
     }
 #pragma unroll
     for (int j = 0; j < IPT; ++j) sp[pidx<A>(tid + j * THREADS)] = v[j] * to_acc(load_x<V, HOTX>(x, xs, hotCols, c[j]));
@@ -396,24 +412,23 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
     const int q0 = tid + (headOpen ? 1 : 0);  // the row this thread stores first in the epilogue
     const int rz = (out.nzRow && q0 < nEmit) ? __ldg(out.nzRow + r0 + q0) : r0 + q0;
     tile_sync<GROUPS>(grp);
-    if (e0 >= 0) {
-        atomicOr(&sFlag[e0 >> 5], 1u << (e0 & 31));
-        atomicMin(&sFirst[e0 >> 5], tid);
-    }
-    if (e1 >= 0) {
-        atomicOr(&sFlag[e1 >> 5], 1u << (e1 & 31));
-        atomicMin(&sFirst[e1 >> 5], tid + THREADS);
-    }
-    for (int k0 = tid + 2 * THREADS; k0 < nEmit; k0 += 4 * THREADS) {  // further row ends, four loads in flight
+    auto mark_end = [&](int e, int row) {  // rows are non-empty, so ends are distinct positions
+        if constexpr (DENSE) {
+            sm.sEnd[e] = 1;
+        } else {
+            atomicOr(&sFlag[e >> 5], 1u << (e & 31));
+            atomicMin(&sFirst[e >> 5], row);
+        }
+    };
+    if (e0 >= 0) mark_end(e0, tid);
+    if (e1 >= 0) mark_end(e1, tid + THREADS);
+    for (int kk = tid + 2 * THREADS; kk < nEmit; kk += 4 * THREADS) {  // further row ends, four loads in flight
         int e[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) e[j] = k0 + j * THREADS < nEmit ? __ldg(ce + 1 + k0 + j * THREADS) - base - 1 : -1;
+        for (int j = 0; j < 4; ++j) e[j] = kk + j * THREADS < nEmit ? __ldg(ce + 1 + kk + j * THREADS) - base - 1 : -1;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            if (e[j] >= 0) {
-                atomicOr(&sFlag[e[j] >> 5], 1u << (e[j] & 31));
-                atomicMin(&sFirst[e[j] >> 5], k0 + j * THREADS);
-            }
+            if (e[j] >= 0) mark_end(e[j], kk + j * THREADS);
     }
     tile_sync<GROUPS>(grp);
 
@@ -440,12 +455,34 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
             }
         }
     }
-    const unsigned word = sFlag[a >> 5];
-    const unsigned mask = (word >> (a & 31)) & ((1u << IPT) - 1u);
+    // mask: bit j set when a row ends at this thread's j-th product; k0: the row (relative to r0) its first bit closes
+    unsigned mask = 0u;
+    int k0 = 0;
+    if constexpr (DENSE) {
+#pragma unroll
+        for (int q = 0; q < IPT / 4; ++q) {  // four end bytes become four bits with one multiply
+            const unsigned wv = reinterpret_cast<const unsigned *>(sm.sEnd + a)[q];
+            mask |= (((wv * 0x01020408u) >> 24) & 0xfu) << (4 * q);
+        }
+        // k0 = row ends before this thread's first product: scan of the threads' counts
+        const int myEnds = __popc(mask);
+        int endsIncl = myEnds;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, endsIncl, d);
+            if (lane >= d) endsIncl += o;
+        }
+        if (lane == 31) sm.warpEnds[w] = endsIncl;
+        k0 = endsIncl - myEnds;
+    } else {
+        const unsigned word = sFlag[a >> 5];
+        mask = (word >> (a & 31)) & ((1u << IPT) - 1u);
+        k0 = sFirst[a >> 5] + __popc(word & ((1u << (a & 31)) - 1u));
+    }
     const bool hasEnd = mask != 0u;
-    // row (relative to r0) closed by this thread's first set bit
-    const int k0 = sFirst[a >> 5] + __popc(word & ((1u << (a & 31)) - 1u));
     tile_sync<GROUPS>(grp);  // every product is in registers: the buffer now holds row sums
+    if constexpr (DENSE)
+        for (int u = 0; u < w; ++u) k0 += sm.warpEnds[u];
     int k = k0;
     A acc = A(0);
 #pragma unroll
@@ -579,16 +616,17 @@ __device__ __forceinline__ void resid_tile(const int t, const int tid, const int
 }
 
 
-template <typename V, int IPT, bool HAS_TILE, int MODE>
+template <typename V, int IPT, bool HAS_TILE, int MODE, bool DENSE = false>
 __global__ void __launch_bounds__(RESID_THREADS, ResidCfg<V>::MINBLOCKS)
     resid_kernel(const int *__restrict__ cPtr, const int *__restrict__ colInd, const V *__restrict__ val,
                  const V *__restrict__ x, RowOut<V> out, const int *__restrict__ tileRow,
                  typename AccOf<V>::T *__restrict__ carry, typename AccOf<V>::T *__restrict__ head, int nnz,
                  int prefetchTiles) {
-    __shared__ TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32> sm;
+    __shared__ TileSmem<typename AccOf<V>::T, RESID_THREADS * IPT, RESID_THREADS / 32, DENSE> sm;
     dep_release();  // the fix-up launch may become resident; it waits for this grid to finish
-    resid_tile<V, IPT, HAS_TILE, MODE, 1, false>(blockIdx.x, threadIdx.x, 0, (int)gridDim.x, sm, nullptr, 0, cPtr,
-                                                 colInd, val, x, out, tileRow, carry, head, nnz, prefetchTiles);
+    resid_tile<V, IPT, HAS_TILE, MODE, 1, false, DENSE>(blockIdx.x, threadIdx.x, 0, (int)gridDim.x, sm, nullptr, 0,
+                                                        cPtr, colInd, val, x, out, tileRow, carry, head, nnz,
+                                                        prefetchTiles);
 }
 
 // The same product with the hot-column prefix of x in shared memory.  In the extraction's column numbering the first
@@ -755,6 +793,10 @@ cudaError_t resid_spmv_t(const ResidPlan &P, const void *x, void *y, const void 
                                     (const int *)P.tile_row, (A *)P.carry, (A *)P.head, P.nnz, P.prefetch_tiles,    \
                                     P.num_tiles, hot, P.dev_err);                                                    \
             }                                                                                                       \
+        } else if (P.dense_row_ends && !HT && MD == OUT_Y) {                                                        \
+            le = launch_chained(resid_kernel<V, IPT, false, OUT_Y, true>, grid, block, s, chained, 0, P.c_ptr,      \
+                                P.col_ind, (const V *)P.val, (const V *)x, out, (const int *)P.tile_row,           \
+                                (A *)P.carry, (A *)P.head, P.nnz, P.prefetch_tiles);                                \
         } else {                                                                                                    \
             le = launch_chained(resid_kernel<V, IPT, HT, MD>, grid, block, s, chained, 0, P.c_ptr, P.col_ind,       \
                                 (const V *)P.val, (const V *)x, out, (const int *)P.tile_row, (A *)P.carry,        \

@@ -56,6 +56,8 @@ struct ResidPlan {
     int hot_cols = 0;                // > 0: x[0, hot_cols) is the hot-column prefix of a permuted x; the persistent kernel
                                      // keeps it in shared memory (a multiple of 16 bytes of values)
     int *dev_err = nullptr;          // device error word for bounded waits (may be null)
+    bool dense_row_ends = false;     // a tile closes hundreds of rows: the plain product marks row ends with bytes and
+                                     // a scan instead of shared-memory atomics (the column-slab passes)
     int m_rows = 0, n_empty = 0;     // non-empty / empty rows
     const int *c_ptr = nullptr;      // [m_rows+1] row pointers of the non-empty rows (= row_ptr when none is empty)
     int *c_ptr_own = nullptr;        // storage of c_ptr when it is not row_ptr
