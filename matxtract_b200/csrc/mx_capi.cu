@@ -311,7 +311,8 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
                         bool permute = true, void *const *peers = nullptr, int n_peers = 0, long long row_offset = 0,
                         void *mc_y = nullptr) {
     if (peers && h->use_slabs && !h->stats.active) {
-        // far passes accumulate into this GPU's own rows of its own y; the band pass, last, sends the finished rows
+        // the far passes' sums go into this GPU's own rows of its own y; the band follows in row ranges whose
+        // finished rows a second stream sends to the other GPUs
         int self = -1;
         for (int g = 0; g < n_peers && self < 0; ++g) {
             cudaPointerAttributes at{};
@@ -324,8 +325,7 @@ static int spmv_enqueue(mx_handle_t h, const void *x_dev, void *y_dev, bool do_t
         const size_t vb = val_bytes(h->dtype);
         void *y_own = static_cast<char *>(peers[self]) + (size_t)row_offset * vb;
         if (h->slabs.has_band) {
-            HCK(col_slabs_spmv_peers(h->dtype, h->slabs, x_dev, y_own, vb * (size_t)h->n_rows, peers, n_peers,
-                                     row_offset, h->stream));
+            HCK(col_slabs_spmv_peers(h->dtype, h->slabs, x_dev, peers, n_peers, self, row_offset, h->stream));
             return MX_OK;
         }
         // no band (the slab spans all columns' rows): accumulate locally, then push the finished rows

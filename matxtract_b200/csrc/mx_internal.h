@@ -87,6 +87,15 @@ struct ColSlabs {
     unsigned char *present = nullptr;  // [(count+7)/8][n_rows]: bit k%8 of plane k/8 set when the row has entries in slab k
     int *group_base = nullptr;   // [ceil(n_rows/32)][count]: non-empty rows of slab k before the group's first row
     int n_rows = 0;
+    // the band once more as `band_chunks` row ranges of equal non-zero count, each with a plan of its own (views into
+    // near_col / near_val with rebased row pointers): through mx_spmv_peers the ranges are multiplied one after the
+    // other and every finished range is sent to the other GPUs from a second stream while the next is computed
+    int band_chunks = 0;
+    ResidPlan *chunk_plans = nullptr;  // [band_chunks]
+    int *chunk_row_ptr = nullptr;      // storage of the rebased row pointers
+    int *chunk_rows = nullptr;         // host [band_chunks + 1] row boundaries
+    cudaStream_t send_stream = nullptr;
+    cudaEvent_t *chunk_done = nullptr; // [band_chunks + 1]; the last: everything has been sent
 };
 
 // Plain CSR on the device (non-owning view).
@@ -193,13 +202,15 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s);
 int col_slabs_launches(const ColSlabs &S);
 // y = A x (value type): the band pass writes every row (without a band y is cleared), every slab adds its part.
 cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
-// one GPU's share of a row-partitioned product: far passes accumulate in y_own, the band pass comes last and stores
-// the finished rows into every GPU's buffer
-cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *y_own, size_t y_bytes,
-                                 void *const *peers, int n_peers, long long row_offset, cudaStream_t s);
-// y_peer[g][row_offset + r] = y_own[r] + row r of the plan's matrix, for every g (y_own = this GPU's rows so far)
-cudaError_t resid_spmv_peers_accum(int dtype, const ResidPlan &plan, const void *x, void *y_own, void *const *peers,
-                                   int n_peers, long long row_offset, cudaStream_t s, bool chained);
+// one GPU's share of a row-partitioned product: the far passes' sums are combined into this GPU's rows of
+// peers[self], the band follows in row ranges, and every finished range is sent to the other GPUs' buffers from a
+// second stream; on return the stream s is ordered after the last send
+cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *const *peers, int n_peers, int self,
+                                 long long row_offset, cudaStream_t s);
+// rows [row_offset, row_offset + n_rows) of peers[self] -> the same rows of every other buffer (16-byte stores over
+// NVLink; byte stores for ragged ends)
+cudaError_t peer_push_rows(int dtype, void *const *peers, int n_peers, int self, long long row_offset, long long n_rows,
+                           cudaStream_t s);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
 void tile_plan_free(TilePlan &plan, cudaStream_t s);
