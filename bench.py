@@ -699,7 +699,7 @@ def run_ours(args):
     else:
         dom, dom_ms, dom_bytes = "resid_kernel(+fixup)", halves["ms_resid"], b_resid
         if slabs[0] > 0:
-            dom = f"resid_kernel(+fixup): band pass + {slabs[0]} column-slab passes"
+            dom = f"resid_kernel(+fixup) x {slabs[0]} column-slab passes + k_combine" + (" + band" if world > 1 else "")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     traffic, traffic_note = (profiled_traffic(cfg.name, dom, tau, n_total) if world == 1 else (None, "N > 1: not captured"))
     if slabs[0] > 0 and traffic is not None:

@@ -267,14 +267,6 @@ __device__ __forceinline__ int pidx(int i) {
 __device__ __forceinline__ void dep_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-static bool chain_enabled() {
-    static const bool on = [] {
-        const char *e = getenv("MX_CHAIN_LAUNCHES");
-        return e ? atoi(e) != 0 : true;
-    }();
-    return on;
-}
-
 template <typename... KArgs, typename... Args>
 cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, bool chained, size_t smem,
                            Args... args) {
@@ -287,7 +279,7 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cuda
     at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &at;
-    cfg.numAttrs = chained && chain_enabled() ? 1 : 0;
+    cfg.numAttrs = chained ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

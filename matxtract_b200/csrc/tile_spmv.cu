@@ -123,7 +123,7 @@ struct CtaDesc {  // computed at plan time
 
 constexpr int STAGE_WARPS = 4;   // warps per CTA (8 measured slower)
 int g_tile_prefetch = -1;        // L2 prefetch distance in CTAs; default 5 per SM (A/B on the block matrix: tile half
-                                 // 113.8 -> 108.7 us; 10 per SM 110.1, 20 per SM 122.8), MX_TILE_PREFETCH overrides, 0 = off
+                                 // 113.8 -> 108.7 us; 10 per SM 110.1, 20 per SM 122.8); 0 = off
 constexpr int STAGE_BYTES_TARGET = 16 * 1024;  // per CTA; a CTA may exceed it by one segment (sweep: 8-64 KB)
 
 // byte layout of a CTA's shared-memory stage; every range starts 16-byte aligned in global AND shared memory
@@ -528,9 +528,7 @@ cudaError_t tile_plan_build(int dtype, TilePlan &P, cudaStream_t s) {
         cudaSuccess)
         return e;
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
-    if (const char *ev = getenv("MX_TILE_PREFETCH")) {
-        g_tile_prefetch = atoi(ev) > 0 ? atoi(ev) : 0;
-    } else if (g_tile_prefetch < 0) {
+    if (g_tile_prefetch < 0) {
         int dev = 0, sms = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

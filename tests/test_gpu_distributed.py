@@ -56,6 +56,33 @@ for name, n, tau in (("c2", 60000, (0.46, 0.33)), ("c3", 8 * 4000, (0.5, 0.5)), 
     del y, x
     d.close()
     print(f"rank {rank} {name} ok err={err:.2e} rows={d.rows} nnz={d.local_nnz}", flush=True)
+# column slabs on a row slab: far passes, combined sums, then the band in row ranges whose finished rows a second
+# stream sends to the other GPU while the next range is computed; the same through slab passes + one copy
+m = synth.generate("c5", n=1_200_000)
+n = m["n"]
+x = torch.from_numpy(m["x"]).cuda()
+want = oracle.exact_spmv(m["row_ptr"], m["col_ind"], m["val"], m["x"])
+scale = oracle.abs_rowsum_max(mx.FP64, m["row_ptr"], m["col_ind"], m["val"], m["x"])
+got = {}
+for how in ("epilogue", "push"):
+    f = D.DistributedSpMV(mx.FP64, n, m["row_ptr"], m["col_ind"], m["val"], rank, world, tau=(0.0, 0.0), fused=how)
+    f.handle.set_column_slabs(6)
+    assert f.handle.column_slabs[0] == 6
+    f.stream.wait_stream(torch.cuda.current_stream())
+    for _ in range(3):
+        yf = f.spmv(x)
+    f.stream.synchronize()
+    got[how] = yf.cpu().numpy()
+    assert np.abs(got[how] - want).max() / scale <= 1e-12, how
+    ck = torch.from_numpy(got[how].view(np.int64)).sum().reshape(1).cuda()
+    cks = [torch.zeros_like(ck) for _ in range(world)]
+    dist.all_gather(cks, ck)
+    assert all(int(c) == int(cks[0]) for c in cks), how  # both GPUs hold the same bits
+    del yf
+    f.close()
+# (the two cut the band into tiles at different places, so rows that span tiles are summed in a different order)
+assert np.abs(got["epilogue"] - got["push"]).max() <= 1e-13 * scale
+print(f"rank {rank} c5-slabs ok", flush=True)
 dist.destroy_process_group()
 '''
 
@@ -77,3 +104,4 @@ def test_two_rank_row_partition_matches_the_oracle(tmp_path):
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count(" ok ") == 8
+    assert r.stdout.count("c5-slabs ok") == 2
