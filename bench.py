@@ -402,6 +402,8 @@ def run_ours(args):
             return partition_with_global_rankings(h, tau, bounds, rank, nnz_total, dev)
         return h.partition(*tau)
 
+    if args.colslabs != -1:  # a forced slab count: mx_partition then builds that layout and times no alternative
+        h.set_column_slabs(args.colslabs)
     st = extract()
     preprocess_ms_cold = st.preprocess_ms  # first call: includes CUDA module loading and memory-pool growth
     st = extract()                         # steady-state cost of the same extraction
@@ -410,8 +412,6 @@ def run_ours(args):
         h.set_dd_executor({"tile": mx.DD_TILE, "csr": mx.DD_CSR, "se": mx.DD_SE}[args.dd])
     if args.colspace != "auto":
         h.set_column_space({"permuted": mx.COLSPACE_PERMUTED, "original": mx.COLSPACE_ORIGINAL}[args.colspace])
-    if args.colslabs != -1:
-        h.set_column_slabs(args.colslabs)
     slabs = h.column_slabs
     if args.hotx != "auto":
         h.set_hot_prefix({"off": mx.HOT_OFF, "on": mx.HOT_ON}[args.hotx])

@@ -36,6 +36,7 @@ namespace {
 inline int nblk(long long n, int b = 256) { return (int)((n + b - 1) / b); }
 
 constexpr int COL_SLAB_HALO = 1 << 16;  // columns on either side of the diagonal that count as the band
+constexpr int MAX_COL_SLABS = 64;       // mx_set_column_slabs accepts at most this many
 constexpr int BAND_CHUNKS = 4;          // row ranges of the band whose sends overlap the next range's kernels (2 GPUs:
                                         // 1 range 3.47 ms, 2: 3.41, 4: 3.28, 8: 3.31)
 
@@ -190,7 +191,10 @@ __global__ void k_presence(const int *__restrict__ flag, const int *__restrict__
 // (Measured and rejected on the 1e9-non-zero shape: four groups of 32 rows per warp with all 32 loads of a lane in
 // flight, 102 registers: +0.41 ms; a warp walking 8 consecutive groups with the next group's presence bits requested
 // ahead: +0.12 ms.  Column slabs exist for FP64 only: the passes and this kernel add in the value type.)
-__global__ void __launch_bounds__(256) k_combine(const double *const *__restrict__ part,
+struct PartTable {
+    const double *p[MAX_COL_SLABS];  // partial sums of every slab (kernel parameter: read through the constant bank)
+};
+__global__ void __launch_bounds__(256) k_combine(const __grid_constant__ PartTable part,
                                                  const unsigned char *__restrict__ present,
                                                  const int *__restrict__ group_base, int count, int n,
                                                  double *__restrict__ y) {
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(256) k_combine(const double *const *__restrict
             const unsigned b = __ballot_sync(0xffffffffu, bit);
             const int bj = __shfl_sync(0xffffffffu, base, j);
             v[j] = 0.0;
-            if (bit) v[j] = __ldg(part[k0 + j] + bj + __popc(b & below));
+            if (bit) v[j] = __ldg(part.p[k0 + j] + (bj + __popc(b & below)));
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -431,8 +435,10 @@ cudaError_t combine(int dtype, const ColSlabs &S, void *y, cudaStream_t s) {
     if (S.n_rows <= 0) return cudaSuccess;
     const int grid = (S.n_rows + 255) / 256;
     if (dtype != MX_FP64) return cudaErrorNotSupported;
-    k_combine<<<grid, 256, 0, s>>>((const double *const *)S.part_table, S.present, S.group_base, S.count, S.n_rows,
-                                   (double *)y);
+    if (S.count > MAX_COL_SLABS) return cudaErrorInvalidValue;
+    PartTable T{};
+    for (int k = 0; k < S.count; ++k) T.p[k] = static_cast<const double *>(S.part[k]);
+    k_combine<<<grid, 256, 0, s>>>(T, S.present, S.group_base, S.count, S.n_rows, (double *)y);
     return cudaGetLastError();
 }
 

@@ -457,8 +457,9 @@ static int tune_col_slabs(mx_handle_t h) {
         return MX_OK;
     }
     if (l2 <= 0 || xbytes <= (size_t)l2) return MX_OK;  // x fits L2: nothing to gain
-    // candidates: x ranges of 96, 64 and 32 MB per pass (fewer passes re-read y less often, narrower ones sit in L2
-    // more safely); each is built, timed against the plain kernel on scratch vectors, and the fastest stays
+    // candidates: x ranges of 64, 44 and 32 MB per pass (fewer passes leave fewer partial sums to combine, narrower
+    // ones keep their x range in L2 more safely; 96 MB never won); each is built, timed against the plain kernel on
+    // scratch vectors, and the fastest stays
     EventPair ev;
     HCK(ev.create());
     HCK(cudaMemsetAsync(h->x_stage, 0, xbytes, h->stream));
@@ -478,7 +479,7 @@ static int tune_col_slabs(mx_handle_t h) {
     if (st != MX_OK) return st;
     float best = h->slab_ms_plain;
     int best_count = 0, last = 0;
-    for (size_t mb : {96, 64, 32}) {
+    for (size_t mb : {64, 44, 32}) {
         const int count = (int)std::min<size_t>(64, (xbytes + (mb << 20) - 1) / (mb << 20));
         if (count < 2 || count == last) continue;
         last = count;
