@@ -11,13 +11,13 @@
 // A pass is the ordinary CSR kernel (resid_kernel) over the slab's NON-EMPTY rows as if they were a dense row space:
 // it writes one partial sum per such row into a buffer of its own, sequentially, and reads nothing but the slab and
 // x.  (Adding into y instead made every pass read and write the whole of y, a sector at a time, through a row-index
-// table: on the 1e9-non-zero shape 8 GB of the product's 28 GB of DRAM traffic.)  A last kernel (k_combine) walks the
-// rows once: a presence bit per (row, slab) and one base count per (32 rows, slab) locate every row's partial sums,
-// which it adds in slab order - the same order of additions as accumulating pass by pass, without atomics and
-// bit-reproducible.  A whole (square) matrix has no band: its near-diagonal entries stay in the slabs.  One GPU's
-// share of a row-partitioned matrix has one: the combined far sums land in its own rows and the band pass runs LAST,
-// adding them and storing the finished rows into every GPU's y from its epilogue, so that the exchange overlaps
-// the pass that holds about half of the work.
+// table: on the 1e9-non-zero shape 8 GB of the product's 28 GB of DRAM traffic.)  A last kernel (k_combine) adds every
+// row's partial sums in slab order - the same order of additions as accumulating pass by pass, without atomics and
+// bit-reproducible: a CTA holds the sums of a block of rows in shared memory and streams, slab by slab, the block's
+// contiguous share of the slab's partial sums with a 2-byte row index each.  A whole (square) matrix has no band: its
+// near-diagonal entries stay in the slabs.  One GPU's share of a row-partitioned matrix has one: the combined far
+// sums land in its own rows, the band follows in row ranges and every finished range is sent to the other GPUs from
+// a second stream, so that the exchange overlaps the band, about half of the work.
 // The reference has no counterpart: it runs one CSR kernel over the whole matrix (src/spmv_kernel/cdSpMV.cu:395-491).
 #include <algorithm>
 
@@ -176,50 +176,54 @@ __global__ void k_rebase(const int *__restrict__ rp, int r0, int len, int *__res
     if (i <= len) out[i] = rp[r0 + i] - rp[r0];
 }
 
-// slab k of the presence tables: flag[r] = the row has entries in the slab, pos = exclusive scan of flag
-__global__ void k_presence(const int *__restrict__ flag, const int *__restrict__ pos, int n, int k, int count,
-                           unsigned char *__restrict__ present, int *__restrict__ group_base) {
+// slab k of the combining kernel's tables: flag[r] = the row has entries in the slab, pos = exclusive scan of flag.
+// The i-th non-empty row of the slab records where it sits inside its block of COMBINE_ROWS rows; every block records
+// how many of the slab's non-empty rows precede it (one entry more than blocks: the total).
+__global__ void k_row_in_block(const int *__restrict__ flag, const int *__restrict__ pos, int n, int k, int count,
+                               unsigned short *__restrict__ row_in_block, int *__restrict__ block_base) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= n) return;
-    if (flag[r]) present[(size_t)(k >> 3) * n + r] |= (unsigned char)(1u << (k & 7));  // one thread per row: no race
-    if ((r & 31) == 0) group_base[(size_t)(r >> 5) * count + k] = pos[r];
+    if (r > n) return;
+    if (r < n && flag[r]) row_in_block[pos[r]] = (unsigned short)(r % COMBINE_ROWS);
+    if (r % COMBINE_ROWS == 0 || r == n) block_base[(size_t)((r + COMBINE_ROWS - 1) / COMBINE_ROWS) * count + k] = pos[r];
 }
 
 // y[r] = sum over the slabs, in slab order, of the partial sum of row r (where the row has entries in the slab).
-// One lane per row: a ballot over the row's presence bit gives the lane's position among the warp's 32 rows, the
-// group's base count the position of the warp's first row, so consecutive present rows read consecutive partial sums.
-// (Measured and rejected on the 1e9-non-zero shape: four groups of 32 rows per warp with all 32 loads of a lane in
-// flight, 102 registers: +0.41 ms; a warp walking 8 consecutive groups with the next group's presence bits requested
-// ahead: +0.12 ms.  Column slabs exist for FP64 only: the passes and this kernel add in the value type.)
+// A CTA owns COMBINE_ROWS consecutive rows and keeps their sums in shared memory.  Slab by slab it streams the block's
+// share of the slab's partial sums - a contiguous range, because a pass writes them in row order - together with each
+// one's row index inside the block (2 bytes) and adds it to that row's sum; a row occurs at most once per slab, so
+// the adds of one slab never collide, and a barrier separates the slabs: every row adds its partial sums in slab
+// order, the same additions in the same order as accumulating pass by pass, without atomics.  Coalesced loads, about
+// eight instructions per partial sum.  (First version: one lane per row, a presence bit per (row, slab) and a warp
+// ballot per slab to find each row's partial sum: 180-350 instructions per 32 rows, issue-bound, 0.95 ms of a 5.5 ms
+// product on the 1e9-non-zero shape with 12 slabs.  Column slabs exist for FP64 only: the passes and this kernel add
+// in the value type.)
 struct PartTable {
-    const double *p[MAX_COL_SLABS];  // partial sums of every slab (kernel parameter: read through the constant bank)
+    const double *p[MAX_COL_SLABS];          // partial sums of every slab (kernel parameters: constant bank)
+    const unsigned short *row[MAX_COL_SLABS]; // their rows' indices inside their blocks
 };
 __global__ void __launch_bounds__(256) k_combine(const __grid_constant__ PartTable part,
-                                                 const unsigned char *__restrict__ present,
-                                                 const int *__restrict__ group_base, int count, int n,
+                                                 const int *__restrict__ block_base, int count, int n,
                                                  double *__restrict__ y) {
-    const int r = blockIdx.x * 256 + threadIdx.x, lane = threadIdx.x & 31;
-    const bool live = r < n;
-    const unsigned below = (1u << lane) - 1u;
-    double acc = 0.0;
-    for (int k0 = 0; k0 < count; k0 += 8) {
-        const unsigned m = live ? (unsigned)__ldg(present + (size_t)(k0 >> 3) * n + r) : 0u;
-        int base = 0;
-        if (lane < 8 && k0 + lane < count && (r - lane) < n) base = __ldg(group_base + (size_t)(r >> 5) * count + k0 + lane);
-        double v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const bool bit = (m >> j) & 1u;
-            const unsigned b = __ballot_sync(0xffffffffu, bit);
-            const int bj = __shfl_sync(0xffffffffu, base, j);
-            v[j] = 0.0;
-            if (bit) v[j] = __ldg(part.p[k0 + j] + (bj + __popc(b & below)));
+    __shared__ double acc[COMBINE_ROWS];
+    const int tid = threadIdx.x;
+    const long long r0 = (long long)blockIdx.x * COMBINE_ROWS;
+    for (int i = tid; i < COMBINE_ROWS; i += 256) acc[i] = 0.0;
+    const int *bb = block_base + (size_t)blockIdx.x * count;
+    __syncthreads();
+    for (int k = 0; k < count; ++k) {
+        const int lo = __ldg(bb + k), len = __ldg(bb + count + k) - lo;
+        const double *__restrict__ p = part.p[k] + lo;
+        const unsigned short *__restrict__ row = part.row[k] + lo;
+        int i = tid;
+        for (; i + 768 < len; i += 1024) {  // four independent loads in flight per thread
+            const double v0 = __ldg(p + i), v1 = __ldg(p + i + 256), v2 = __ldg(p + i + 512), v3 = __ldg(p + i + 768);
+            const int q0 = __ldg(row + i), q1 = __ldg(row + i + 256), q2 = __ldg(row + i + 512), q3 = __ldg(row + i + 768);
+            acc[q0] += v0, acc[q1] += v1, acc[q2] += v2, acc[q3] += v3;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if ((m >> j) & 1u) acc += v[j];  // a row's absent slabs add nothing (not even +0)
+        for (; i < len; i += 256) acc[__ldg(row + i)] += __ldg(p + i);
+        __syncthreads();
     }
-    if (live) y[r] = acc;
+    for (int i = tid; i < COMBINE_ROWS && r0 + i < n; i += 256) y[r0 + i] = acc[i];
 }
 
 template <typename V>
@@ -262,11 +266,9 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
     out.col = new int *[count]();
     out.val = new void *[count]();
     out.part = new void *[count]();
-    const size_t planes = ((size_t)count + 7) / 8, groups = ((size_t)n + 31) / 32;
-    CS_TRY(cudaMallocAsync(&out.present, std::max<size_t>(planes * (size_t)n, 1), s));
-    CS_TRY(cudaMemsetAsync(out.present, 0, std::max<size_t>(planes * (size_t)n, 1), s));
-    CS_TRY(cudaMallocAsync(&out.group_base, std::max<size_t>(groups * count, 1) * sizeof(int), s));
-    CS_TRY(cudaMallocAsync(&out.part_table, (size_t)count * sizeof(void *), s));
+    out.row_in_block = new unsigned short *[count]();
+    const size_t blocks = ((size_t)n + COMBINE_ROWS - 1) / COMBINE_ROWS;
+    CS_TRY(cudaMallocAsync(&out.block_base, (blocks + 1) * count * sizeof(int), s));
     // ---- the band: a CSR over all rows.  Only a row slab of a larger matrix (one GPU's share) has one: its band
     //      pass is what sends the finished rows to the other GPUs.  A whole matrix keeps its near-diagonal entries in
     //      the slabs (one pass over y fewer: measured 6.40 against 6.56 ms on the 1e9-nnz shape). ----
@@ -338,7 +340,6 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
                                               len, flag);
         CS_TRY(exclusive_sum(tmp, flag, pos, (int)n1, s));
         CS_TRY(exclusive_sum(tmp, len, off, (int)n1, s));
-        if (n > 0) k_presence<<<nblk(n), 256, 0, s>>>(flag, pos, n, k, count, out.present, out.group_base);
         int m_rows = 0, nnz_slab = 0;
         CS_TRY(cudaMemcpyAsync(&m_rows, pos + n, sizeof(int), cudaMemcpyDeviceToHost, s));
         CS_TRY(cudaMemcpyAsync(&nnz_slab, off + n, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -352,6 +353,8 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         P.dense_row_ends = (long long)m_rows * 16 >= nnz_slab;  // 128 or more row ends per tile of 2048 non-zeros
         CS_TRY(cudaMallocAsync(&P.c_ptr_own, ((size_t)m_rows + 1) * sizeof(int), s));
         CS_TRY(cudaMallocAsync(&out.part[k], (size_t)std::max(m_rows, 1) * sizeof(V), s));
+        CS_TRY(cudaMallocAsync(&out.row_in_block[k], (size_t)std::max(m_rows, 1) * sizeof(unsigned short), s));
+        k_row_in_block<<<nblk(n1), 256, 0, s>>>(flag, pos, n, k, count, out.row_in_block[k], out.block_base);
         CS_TRY(cudaMallocAsync(&out.col[k], (size_t)std::max(nnz_slab, 1) * sizeof(int), s));
         CS_TRY(cudaMallocAsync(&out.val[k], (size_t)std::max(nnz_slab, 1) * sizeof(V), s));
         k_far_copy<V><<<nblk(std::max(n, 1)), 256, 0, s>>>(A.col_ind, (const V *)A.val, lo1, len1, lo2, len2, pos, off, n,
@@ -364,7 +367,6 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         P.val = out.val[k];
         CS_TRY(resid_plan_finish(dtype, P, s));
     }
-    CS_TRY(cudaMemcpyAsync(out.part_table, out.part, (size_t)count * sizeof(void *), cudaMemcpyHostToDevice, s));
     CS_TRY(cudaStreamSynchronize(s));
     return cudaSuccess;
 }
@@ -386,9 +388,9 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s) {
         if (S.col && S.col[k]) cudaFreeAsync(S.col[k], s);
         if (S.val && S.val[k]) cudaFreeAsync(S.val[k], s);
         if (S.part && S.part[k]) cudaFreeAsync(S.part[k], s);
+        if (S.row_in_block && S.row_in_block[k]) cudaFreeAsync(S.row_in_block[k], s);
     }
-    for (void *p : {(void *)S.present, (void *)S.group_base, (void *)S.part_table})
-        if (p) cudaFreeAsync(p, s);
+    if (S.block_base) cudaFreeAsync(S.block_base, s);
     resid_plan_free(S.near, s);
     if (S.send_stream) cudaStreamSynchronize(S.send_stream);
     for (int c = 0; c < S.band_chunks; ++c) resid_plan_free(S.chunk_plans[c], s);
@@ -406,6 +408,7 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s) {
     delete[] S.col;
     delete[] S.val;
     delete[] S.part;
+    delete[] S.row_in_block;
     S = ColSlabs();
 }
 
@@ -433,12 +436,15 @@ cudaError_t far_passes(int dtype, const ColSlabs &S, const void *x, cudaStream_t
 
 cudaError_t combine(int dtype, const ColSlabs &S, void *y, cudaStream_t s) {
     if (S.n_rows <= 0) return cudaSuccess;
-    const int grid = (S.n_rows + 255) / 256;
+    const int grid = (S.n_rows + COMBINE_ROWS - 1) / COMBINE_ROWS;
     if (dtype != MX_FP64) return cudaErrorNotSupported;
     if (S.count > MAX_COL_SLABS) return cudaErrorInvalidValue;
     PartTable T{};
-    for (int k = 0; k < S.count; ++k) T.p[k] = static_cast<const double *>(S.part[k]);
-    k_combine<<<grid, 256, 0, s>>>(T, S.present, S.group_base, S.count, S.n_rows, (double *)y);
+    for (int k = 0; k < S.count; ++k) {
+        T.p[k] = static_cast<const double *>(S.part[k]);
+        T.row[k] = S.row_in_block[k];
+    }
+    k_combine<<<grid, 256, 0, s>>>(T, S.block_base, S.count, S.n_rows, (double *)y);
     return cudaGetLastError();
 }
 

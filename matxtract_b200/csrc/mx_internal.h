@@ -72,6 +72,7 @@ struct ResidPlan {
 // far entries cut into vertical slabs of `width` columns, each a CSR of its own over its non-empty rows and multiplied
 // in a pass of its own, so that the x range a pass gathers from stays resident in L2.  A pass writes one partial sum
 // per non-empty row of its slab, densely; a last kernel adds every row's partial sums in slab order.  Owned.
+constexpr int COMBINE_ROWS = 2048;  // rows whose sums one CTA of the combining kernel holds in shared memory
 struct ColSlabs {
     int count = 0, width = 0, halo = 0;
     long long row_offset = 0;    // global index of the matrix's first row (a row slab of a larger square matrix)
@@ -83,9 +84,9 @@ struct ColSlabs {
     int **col = nullptr;         // [count] host array of device pointers
     void **val = nullptr;        // [count]
     void **part = nullptr;       // [count] host array: partial sums (value type) of slab k's non-empty rows, in row order
-    void **part_table = nullptr; // the same pointers on the device
-    unsigned char *present = nullptr;  // [(count+7)/8][n_rows]: bit k%8 of plane k/8 set when the row has entries in slab k
-    int *group_base = nullptr;   // [ceil(n_rows/32)][count]: non-empty rows of slab k before the group's first row
+    unsigned short **row_in_block = nullptr;  // [count] host array: for slab k's i-th non-empty row, its index inside
+                                              // its block of COMBINE_ROWS consecutive rows
+    int *block_base = nullptr;   // [ceil(n_rows / COMBINE_ROWS) + 1][count]: non-empty rows of slab k before the block
     int n_rows = 0;
     // the band once more as `band_chunks` row ranges of equal non-zero count, each with a plan of its own (views into
     // near_col / near_val with rebased row pointers): through mx_spmv_peers the ranges are multiplied one after the
