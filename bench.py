@@ -701,9 +701,11 @@ def run_ours(args):
         if slabs[0] > 0:
             dom = f"resid_kernel(+fixup) x {slabs[0]} column-slab passes + k_combine" + (" + band" if world > 1 else "")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    traffic, traffic_note = (profiled_traffic(cfg.name, dom, tau, n_total) if world == 1 else (None, "N > 1: not captured"))
+    # the table is keyed without the slab count (the tuner may settle on a neighbouring count from run to run)
+    dom_key = "resid_kernel(+fixup) column-slab passes + k_combine" if slabs[0] > 0 else dom
+    traffic, traffic_note = (profiled_traffic(cfg.name, dom_key, tau, n_total) if world == 1 else (None, "N > 1: not captured"))
     if slabs[0] > 0 and traffic is not None:
-        traffic_note += " (sum over the passes of one product)"
+        traffic_note += " (sum over the launches of one product, captured with 12 slabs)"
     eff_gbs = b_alg_total / (ms_step * 1e-3) / 1e9
 
     y_np_of = None
