@@ -16,8 +16,8 @@
 // bit-reproducible: a CTA holds the sums of a block of rows in shared memory and streams, slab by slab, the block's
 // contiguous share of the slab's partial sums with a 2-byte row index each.  A whole (square) matrix has no band: its
 // near-diagonal entries stay in the slabs.  One GPU's share of a row-partitioned matrix has one: the combined far
-// sums land in its own rows, the band follows in row ranges and every finished range is sent to the other GPUs from
-// a second stream, so that the exchange overlaps the band, about half of the work.
+// sums land in its own rows, the band follows in row ranges and the copy engines send every finished range to the
+// other GPUs from a second stream, so that the exchange overlaps the band, about half of the work.
 // The reference has no counterpart: it runs one CSR kernel over the whole matrix (src/spmv_kernel/cdSpMV.cu:395-491).
 #include <algorithm>
 
@@ -37,8 +37,8 @@ inline int nblk(long long n, int b = 256) { return (int)((n + b - 1) / b); }
 
 constexpr int COL_SLAB_HALO = 1 << 16;  // columns on either side of the diagonal that count as the band
 constexpr int MAX_COL_SLABS = 64;       // mx_set_column_slabs accepts at most this many
-constexpr int BAND_CHUNKS = 4;          // row ranges of the band whose sends overlap the next range's kernels (2 GPUs:
-                                        // 1 range 3.47 ms, 2: 3.41, 4: 3.28, 8: 3.31)
+constexpr int BAND_CHUNKS = 4;          // row ranges of the band whose sends overlap the next range's kernels (2 GPUs,
+                                        // 2.79 ms of kernels: 2 ranges 3.02 ms, 4: 2.97, 8: 3.01)
 
 // first position in [lo, hi) whose column is >= c
 __device__ __forceinline__ int lower_col(const int *__restrict__ col, int lo, int hi, int c) {
@@ -464,11 +464,13 @@ cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y,
 
 // The same product as one GPU's share of a row-partitioned matrix: the far passes' partial sums are combined into
 // this GPU's rows of its own full-length buffer; the band follows in row ranges of equal non-zero count (the CSR
-// kernel's accumulate mode), and as soon as a range is finished a copy kernel on a second, high-priority stream sends
-// its rows to the other GPUs' buffers with 16-byte stores while the next range is computed.  The exchange thus
-// overlaps the band, about half of the work.  (Storing the rows to the peers from the band kernel's own epilogue was
-// measured first: once the sends of all SMs saturate NVLink the stores back up into the SMs and stall the gathers
-// behind them - 4 GPUs: 2.56 ms against 2.23 ms for kernels followed by one copy; 8 GPUs: 2.60 against 1.72 ms.)
+// kernel's accumulate mode), and as soon as a range is finished the copy engines send its rows to the other GPUs'
+// buffers (one cudaMemcpyAsync per destination on a second stream) while the next range is computed.  The exchange
+// thus overlaps the band, about half of the work.  Measured before this: the rows stored to the peers from the band
+// kernel's own epilogue - once the stores of all SMs saturate NVLink they back up into the SMs and stall the gathers
+// behind them (4 GPUs: 2.56 ms against 2.23 ms for kernels followed by one copy kernel) - and a copy kernel on the
+// second stream instead of the copy engines, which takes SMs and load/store slots from the band (2 GPUs, 2.79 ms of
+// kernels: 3.04 ms with the kernel on a third of the SMs, 2.97 ms with the copy engines).
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *const *peers, int n_peers, int self,
                                  long long row_offset, cudaStream_t s) {
     if (!S.has_band || S.band_chunks < 1) return cudaErrorNotSupported;  // without a band the caller sends the rows
@@ -484,7 +486,10 @@ cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, vo
             e = resid_spmv(dtype, S.chunk_plans[c], x, y_own + (size_t)r0 * vb, nullptr, nullptr, /*accumulate=*/true, s);
         if (e == cudaSuccess) e = cudaEventRecord(S.chunk_done[c], s);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(S.send_stream, S.chunk_done[c], 0);
-        if (e == cudaSuccess) e = peer_push_rows(dtype, peers, n_peers, self, row_offset + r0, len, S.send_stream);
+        for (int g = 0; g < n_peers && e == cudaSuccess; ++g)  // one copy per destination, by the copy engines
+            if (g != self)
+                e = cudaMemcpyAsync(static_cast<char *>(peers[g]) + (size_t)(row_offset + r0) * vb,
+                                    y_own + (size_t)r0 * vb, (size_t)len * vb, cudaMemcpyDeviceToDevice, S.send_stream);
     }
     if (e == cudaSuccess) e = cudaEventRecord(S.chunk_done[S.band_chunks], S.send_stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s, S.chunk_done[S.band_chunks], 0);

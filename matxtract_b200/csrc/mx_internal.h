@@ -90,7 +90,7 @@ struct ColSlabs {
     int n_rows = 0;
     // the band once more as `band_chunks` row ranges of equal non-zero count, each with a plan of its own (views into
     // near_col / near_val with rebased row pointers): through mx_spmv_peers the ranges are multiplied one after the
-    // other and every finished range is sent to the other GPUs from a second stream while the next is computed
+    // other and every finished range is copied to the other GPUs from a second stream while the next is computed
     int band_chunks = 0;
     ResidPlan *chunk_plans = nullptr;  // [band_chunks]
     int *chunk_row_ptr = nullptr;      // storage of the rebased row pointers
@@ -204,14 +204,10 @@ int col_slabs_launches(const ColSlabs &S);
 // y = A x (value type): the band pass writes every row (without a band y is cleared), every slab adds its part.
 cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
 // one GPU's share of a row-partitioned product: the far passes' sums are combined into this GPU's rows of
-// peers[self], the band follows in row ranges, and every finished range is sent to the other GPUs' buffers from a
-// second stream; on return the stream s is ordered after the last send
+// peers[self], the band follows in row ranges, and the copy engines send every finished range to the other GPUs'
+// buffers from a second stream; on return the stream s is ordered after the last send
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *const *peers, int n_peers, int self,
                                  long long row_offset, cudaStream_t s);
-// rows [row_offset, row_offset + n_rows) of peers[self] -> the same rows of every other buffer (16-byte stores over
-// NVLink; byte stores for ragged ends)
-cudaError_t peer_push_rows(int dtype, void *const *peers, int n_peers, int self, long long row_offset, long long n_rows,
-                           cudaStream_t s);
 
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
 void tile_plan_free(TilePlan &plan, cudaStream_t s);
