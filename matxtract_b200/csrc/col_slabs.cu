@@ -16,8 +16,8 @@
 // bit-reproducible: a CTA holds the sums of a block of rows in shared memory and streams, slab by slab, the block's
 // contiguous share of the slab's partial sums with a 2-byte row index each.  A whole (square) matrix has no band: its
 // near-diagonal entries stay in the slabs.  One GPU's share of a row-partitioned matrix has one: the combined far
-// sums land in its own rows, the band follows in row ranges and the copy engines send every finished range to the
-// other GPUs from a second stream, so that the exchange overlaps the band, about half of the work.
+// sums land in its own rows, the band follows in row ranges and every finished range is sent to the other GPUs from
+// other streams, so that the exchange overlaps the band, about half of the work.
 // The reference has no counterpart: it runs one CSR kernel over the whole matrix (src/spmv_kernel/cdSpMV.cu:395-491).
 #include <algorithm>
 
@@ -309,15 +309,14 @@ cudaError_t build_t(const CsrDev &A, int count, long long row_offset, ColSlabs &
         out.band_chunks = chunks;
         out.chunk_plans = new ResidPlan[chunks];
         out.chunk_rows = new int[chunks + 1];
-        out.chunk_done = new cudaEvent_t[chunks + 1]();
+        out.chunk_done = new cudaEvent_t[chunks]();
         CS_TRY(cudaMallocAsync(&out.chunk_row_ptr, ((size_t)n + chunks) * sizeof(int), s));
-        int prio_lo = 0, prio_hi = 0;
-        CS_TRY(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
-        CS_TRY(cudaStreamCreateWithPriority(&out.send_stream, cudaStreamNonBlocking, prio_hi));
-        for (int c = 0; c <= chunks; ++c) {
-            out.chunk_rows[c] = hb[c];
-            CS_TRY(cudaEventCreateWithFlags(&out.chunk_done[c], cudaEventDisableTiming));
+        for (int i = 0; i < ColSlabs::SEND_STREAMS; ++i) {
+            CS_TRY(cudaStreamCreateWithFlags(&out.send_stream[i], cudaStreamNonBlocking));
+            CS_TRY(cudaEventCreateWithFlags(&out.send_done[i], cudaEventDisableTiming));
         }
+        for (int c = 0; c <= chunks; ++c) out.chunk_rows[c] = hb[c];
+        for (int c = 0; c < chunks; ++c) CS_TRY(cudaEventCreateWithFlags(&out.chunk_done[c], cudaEventDisableTiming));
         for (int c = 0; c < chunks; ++c) {
             const int r0 = hb[c], len = hb[c + 1] - r0, e0 = hb[chunks + 1 + c], e1 = hb[chunks + 1 + c + 1];
             int *rp = out.chunk_row_ptr + r0 + c;
@@ -392,12 +391,16 @@ void col_slabs_free(ColSlabs &S, cudaStream_t s) {
     }
     if (S.block_base) cudaFreeAsync(S.block_base, s);
     resid_plan_free(S.near, s);
-    if (S.send_stream) cudaStreamSynchronize(S.send_stream);
+    for (cudaStream_t q : S.send_stream)
+        if (q) cudaStreamSynchronize(q);
     for (int c = 0; c < S.band_chunks; ++c) resid_plan_free(S.chunk_plans[c], s);
     if (S.chunk_done)
-        for (int c = 0; c <= S.band_chunks; ++c)
+        for (int c = 0; c < S.band_chunks; ++c)
             if (S.chunk_done[c]) cudaEventDestroy(S.chunk_done[c]);
-    if (S.send_stream) cudaStreamDestroy(S.send_stream);
+    for (int i = 0; i < ColSlabs::SEND_STREAMS; ++i) {
+        if (S.send_done[i]) cudaEventDestroy(S.send_done[i]);
+        if (S.send_stream[i]) cudaStreamDestroy(S.send_stream[i]);
+    }
     if (S.chunk_row_ptr) cudaFreeAsync(S.chunk_row_ptr, s);
     delete[] S.chunk_plans;
     delete[] S.chunk_rows;
@@ -464,13 +467,12 @@ cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y,
 
 // The same product as one GPU's share of a row-partitioned matrix: the far passes' partial sums are combined into
 // this GPU's rows of its own full-length buffer; the band follows in row ranges of equal non-zero count (the CSR
-// kernel's accumulate mode), and as soon as a range is finished the copy engines send its rows to the other GPUs'
-// buffers (one cudaMemcpyAsync per destination on a second stream) while the next range is computed.  The exchange
-// thus overlaps the band, about half of the work.  Measured before this: the rows stored to the peers from the band
-// kernel's own epilogue - once the stores of all SMs saturate NVLink they back up into the SMs and stall the gathers
-// behind them (4 GPUs: 2.56 ms against 2.23 ms for kernels followed by one copy kernel) - and a copy kernel on the
-// second stream instead of the copy engines, which takes SMs and load/store slots from the band (2 GPUs, 2.79 ms of
-// kernels: 3.04 ms with the kernel on a third of the SMs, 2.97 ms with the copy engines).
+// kernel's accumulate mode), and as soon as a range is finished its rows are sent to the other GPUs' buffers from
+// other streams while the next range is computed - by the copy engines when there is one destination, by a small copy
+// kernel when there are several (see below).  The exchange thus overlaps the band, about half of the work.  Measured
+// before this: the rows stored to the peers from the band kernel's own epilogue - once the stores of all SMs saturate
+// NVLink they back up into the SMs and stall the gathers behind them (4 GPUs: 2.56 ms against 2.23 ms for kernels
+// followed by one copy).
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *const *peers, int n_peers, int self,
                                  long long row_offset, cudaStream_t s) {
     if (!S.has_band || S.band_chunks < 1) return cudaErrorNotSupported;  // without a band the caller sends the rows
@@ -479,20 +481,42 @@ cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, vo
     bool first = true;
     cudaError_t e = far_passes(dtype, S, x, s, first);
     if (e == cudaSuccess) e = combine(dtype, S, y_own, s);
+    // How a finished range leaves.  One destination (2 GPUs): two copies by the copy engines, each on a stream of its
+    // own (one engine moves about 330 GB/s over NVLink; they take no SM from the band: 2.97 ms against 3.04 ms with
+    // the copy kernel, 2.79 ms of kernels).  Several destinations: one launch of the copy kernel on a third of the
+    // SMs, which keeps all links busy at once (4 GPUs, 1.49 ms of kernels: 2.10 ms against 2.17 ms with one engine
+    // copy per destination).
+    const int nd = n_peers - 1;
+    const bool by_kernel = nd >= 2;
+    const int parts = 2, used = by_kernel ? 1 : std::min(ColSlabs::SEND_STREAMS, std::max(nd * parts, 0));
     for (int c = 0; c < S.band_chunks && e == cudaSuccess; ++c) {
         const int r0 = S.chunk_rows[c], len = S.chunk_rows[c + 1] - r0;
         if (len <= 0) continue;
         if (S.chunk_plans[c].nnz > 0)
             e = resid_spmv(dtype, S.chunk_plans[c], x, y_own + (size_t)r0 * vb, nullptr, nullptr, /*accumulate=*/true, s);
+        if (nd <= 0) continue;
         if (e == cudaSuccess) e = cudaEventRecord(S.chunk_done[c], s);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(S.send_stream, S.chunk_done[c], 0);
-        for (int g = 0; g < n_peers && e == cudaSuccess; ++g)  // one copy per destination, by the copy engines
-            if (g != self)
-                e = cudaMemcpyAsync(static_cast<char *>(peers[g]) + (size_t)(row_offset + r0) * vb,
-                                    y_own + (size_t)r0 * vb, (size_t)len * vb, cudaMemcpyDeviceToDevice, S.send_stream);
+        for (int i = 0; i < used && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(S.send_stream[i], S.chunk_done[c], 0);
+        if (by_kernel) {
+            if (e == cudaSuccess) e = peer_push_rows(dtype, peers, n_peers, self, row_offset + r0, len, S.send_stream[0]);
+            continue;
+        }
+        int k = 0;
+        for (int g = 0; g < n_peers && e == cudaSuccess; ++g) {
+            if (g == self) continue;
+            for (int q = 0; q < parts && e == cudaSuccess; ++q, ++k) {
+                const size_t a = (size_t)len * q / parts, b = (size_t)len * (q + 1) / parts;
+                if (b > a)
+                    e = cudaMemcpyAsync(static_cast<char *>(peers[g]) + ((size_t)(row_offset + r0) + a) * vb,
+                                        y_own + ((size_t)r0 + a) * vb, (b - a) * vb, cudaMemcpyDeviceToDevice,
+                                        S.send_stream[k % ColSlabs::SEND_STREAMS]);
+            }
+        }
     }
-    if (e == cudaSuccess) e = cudaEventRecord(S.chunk_done[S.band_chunks], S.send_stream);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, S.chunk_done[S.band_chunks], 0);
+    for (int i = 0; i < used && e == cudaSuccess; ++i) {  // the caller's stream continues after the last copy
+        e = cudaEventRecord(S.send_done[i], S.send_stream[i]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s, S.send_done[i], 0);
+    }
     return e;
 }
 

@@ -95,8 +95,10 @@ struct ColSlabs {
     ResidPlan *chunk_plans = nullptr;  // [band_chunks]
     int *chunk_row_ptr = nullptr;      // storage of the rebased row pointers
     int *chunk_rows = nullptr;         // host [band_chunks + 1] row boundaries
-    cudaStream_t send_stream = nullptr;
-    cudaEvent_t *chunk_done = nullptr; // [band_chunks + 1]; the last: everything has been sent
+    static constexpr int SEND_STREAMS = 2;  // concurrent engine copies to one destination (or stream 0: the copy kernel)
+    cudaStream_t send_stream[SEND_STREAMS] = {};
+    cudaEvent_t send_done[SEND_STREAMS] = {};  // a stream's copies have all been issued and finished
+    cudaEvent_t *chunk_done = nullptr;         // [band_chunks]: the range's rows are final
 };
 
 // Plain CSR on the device (non-owning view).
@@ -204,11 +206,15 @@ int col_slabs_launches(const ColSlabs &S);
 // y = A x (value type): the band pass writes every row (without a band y is cleared), every slab adds its part.
 cudaError_t col_slabs_spmv(int dtype, const ColSlabs &S, const void *x, void *y, size_t y_bytes, cudaStream_t s);
 // one GPU's share of a row-partitioned product: the far passes' sums are combined into this GPU's rows of
-// peers[self], the band follows in row ranges, and the copy engines send every finished range to the other GPUs'
-// buffers from a second stream; on return the stream s is ordered after the last send
+// peers[self], the band follows in row ranges, and every finished range is sent to the other GPUs' buffers from
+// other streams; on return the stream s is ordered after the last send
 cudaError_t col_slabs_spmv_peers(int dtype, const ColSlabs &S, const void *x, void *const *peers, int n_peers, int self,
                                  long long row_offset, cudaStream_t s);
 
+// rows [row_offset, row_offset + n_rows) of peers[self] -> the same rows of every other buffer (16-byte stores over
+// NVLink by a copy kernel on a third of the SMs; byte stores for ragged ends)
+cudaError_t peer_push_rows(int dtype, void *const *peers, int n_peers, int self, long long row_offset, long long n_rows,
+                           cudaStream_t s);
 cudaError_t tile_plan_build(int dtype, TilePlan &plan, cudaStream_t s);
 void tile_plan_free(TilePlan &plan, cudaStream_t s);
 // out[row_map ? row_map[i] : i] (accumulate type when out_is_acc, else value type) = tile row i result.
