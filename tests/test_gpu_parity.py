@@ -412,9 +412,8 @@ def test_core_dense_block_through_each_executor(name, n, tau):
 
 def test_column_slab_execution_matches_the_plain_kernel():
     """tau = (0,0), FP64: the product cut into column slabs (one pass per slab writing partial sums, combined in slab
-    order; 16 slabs need two planes of presence bits, and the row count leaves a ragged last group of 32 rows) equals
-    the reference within tolerance, is reproducible bit for bit, and is refused (plain kernel kept) when rows are not
-    sorted by column."""
+    order by blocks of 2048 rows; the row count leaves a ragged last block) equals the reference within tolerance, is
+    reproducible bit for bit, and is refused (plain kernel kept) when rows are not sorted by column."""
     m = synth.generate("c5", n=300_011)
     n, rp, ci, val, x = m["n"], m["row_ptr"], m["col_ind"], m["val"], m["x"]
     h = mx.MatXtract(FP64)
