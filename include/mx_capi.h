@@ -204,7 +204,8 @@ int mx_mg_download_y(mx_mg_t mg, int g, void *y_host);
 /* warm + iters products on device-resident copies of x; *ms_per_spmv = device time of the slowest GPU / iters. */
 int mx_mg_spmv_timed(mx_mg_t mg, const void *x_host, int warm, int iters, float *ms_per_spmv);
 
-/* Same with HOST pointers: copies x in, runs, copies y out, synchronises. */
+/* Same with HOST pointers: copies x in, runs, copies y out, synchronises.  (Products enqueued with
+ * mx_spmv_host_async that are still in flight are waited for first: they share the staging buffers.) */
 int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host);
 /* A sequence of products with HOST pointers, pipelined: the call enqueues "copy x in, multiply, copy y out" and
  * returns; the copy in, the kernels and the copy out of consecutive calls run on three streams over two sets of

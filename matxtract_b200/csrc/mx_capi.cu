@@ -988,6 +988,11 @@ int mx_spmv_host(mx_handle_t h, const void *x_host, void *y_host) {
     if (!h || !x_host || !y_host) return MX_ERR_INVALID;
     if (!h->planned) return h->fail(MX_ERR_STATE, "mx_spmv_host: call mx_partition first");
     HCK(cudaSetDevice(h->device));
+    if (h->copy_in) {  // pipelined products still in flight share the first pair of staging buffers: let them finish
+        HCK(cudaStreamSynchronize(h->copy_in));
+        HCK(cudaStreamSynchronize(h->stream));
+        HCK(cudaStreamSynchronize(h->copy_out));
+    }
     const size_t vb = val_bytes(h->dtype);
     HCK(cudaMemcpyAsync(h->x_stage, x_host, vb * (size_t)h->n_cols, cudaMemcpyHostToDevice, h->stream));
     int st = spmv_enqueue(h, h->x_stage, h->y_stage, true, true);
