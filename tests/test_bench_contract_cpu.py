@@ -40,3 +40,30 @@ def test_reference_arm_prints_one_contract_line():
 def test_reference_arm_is_silent_on_other_ranks():
     r = _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}, "--gpus", "2")
     assert r.returncode == 0 and not [l for l in r.stdout.splitlines() if l.startswith("{")]
+
+
+def test_traffic_comes_from_the_tracked_table_and_names_a_stale_capture(tmp_path, monkeypatch):
+    """roofline.traffic is read from profiles/dram_traffic.md, never typed into the benchmark: a row captured on the
+    current kernel sources says so, a row captured on other sources is flagged, a capture of fewer rows is scaled by
+    the row count, and a workload without a row yields None."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from matxtract_b200.build import source_hash
+
+    (tmp_path / "profiles").mkdir()
+    (tmp_path / "profiles" / "dram_traffic.md").write_text(
+        "| workload | tau | kernel | rows | bytes per launch | source hash | summary |\n|---|---|---|---|---|---|---|\n"
+        f"| c5 | 0,0 | k | 1000 | 5000 | {source_hash()} | a.md |\n"
+        "| c2 | 0.46,0.33 | k | 2000 | 7000 | 0123456789ab | b.md |\n")
+    monkeypatch.setattr(bench, "ROOT", tmp_path)
+    b, note = bench.profiled_traffic("c5", "k", (0.0, 0.0), 1000)
+    assert b == 5000 and "unchanged" in note
+    b, note = bench.profiled_traffic("c5", "k", (0.0, 0.0), 4000)
+    assert b == 20000 and "scaled to 4000 rows" in note
+    b, note = bench.profiled_traffic("c2", "k", (0.46, 0.33), 2000)
+    assert b == 7000 and "CHANGED" in note
+    assert bench.profiled_traffic("c3", "k", (0.5, 0.5), 10)[0] is None
+    # the committed table has a row for the default workload
+    monkeypatch.setattr(bench, "ROOT", ROOT)
+    b, _ = bench.profiled_traffic("c5", "resid_kernel(+fixup) column-slab passes + k_combine", (0.0, 0.0), 64_000_000)
+    assert b and b > 1e10
